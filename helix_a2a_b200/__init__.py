@@ -1,0 +1,39 @@
+"""helix_a2a_b200 — Blackwell-native (B200, sm_100a) Helix context-parallel decode library.
+
+Public API (same four calls as the reference's ``helix_a2a/__init__.py:23-121`` plus the
+fused paths)::
+
+    workspace_size(cp_size) -> int
+    allocate_workspace(cp_size, cp_rank, device="cuda", *, mnnvl=False, cpu_group=None) -> Tensor
+    init_workspace(workspace, cp_rank, cp_size) -> None
+    alltoall(partial_o, softmax_stats, workspace, cp_rank, cp_size) -> (Tensor, Tensor)
+    alltoall_combine(attn_out, lse, workspace, cp_rank, cp_size, ...) -> Tensor
+    check_status / reset_workspace / debug_info
+"""
+from ._version import __version__
+from .api import (
+    HelixTimeoutError,
+    alltoall,
+    alltoall_combine,
+    allocate_workspace,
+    check_status,
+    debug_info,
+    init_workspace,
+    init_workspace_all_rows,
+    reset_workspace,
+    workspace_size,
+)
+
+__all__ = [
+    "workspace_size",
+    "allocate_workspace",
+    "init_workspace",
+    "alltoall",
+    "alltoall_combine",
+    "check_status",
+    "reset_workspace",
+    "debug_info",
+    "init_workspace_all_rows",
+    "HelixTimeoutError",
+    "__version__",
+]

@@ -1,0 +1,60 @@
+"""Environment knobs of the library, all under the ``HELIX_A2A_`` prefix.
+
+The first four keep the names and meanings the reference uses
+(``csrc/helix_alltoall.cu:541-548``, ``csrc/torch_binding.cpp:25-32``,
+``helix_a2a/mnnvl.py:577-607``, ``patches/dcp_alltoall_helix.py:40``); the rest
+are new.  Unlike the reference, values are read on every call (cheap) so tests
+can flip them without re-importing.
+"""
+from __future__ import annotations
+
+import os
+
+_TRUE = ("1", "true", "yes", "on")
+_FALSE = ("0", "false", "no", "off")
+
+
+def enable_pdl() -> bool:
+    """``HELIX_A2A_ENABLE_PDL=1``: launch with programmatic stream serialization."""
+    return os.environ.get("HELIX_A2A_ENABLE_PDL", "0").strip() == "1"
+
+
+def channel_count() -> int:
+    """``HELIX_A2A_CHANNEL_COUNT``: 0 / unset = auto-tune, else a fixed channel count."""
+    v = os.environ.get("HELIX_A2A_CHANNEL_COUNT", "0").strip()
+    try:
+        return max(int(v), 0)
+    except ValueError:
+        return 0
+
+
+def use_mnnvl() -> str:
+    """``HELIX_A2A_USE_MNNVL``: ``"0"`` device memory, ``"1"`` peer-mapped VMM, ``"auto"``."""
+    v = os.environ.get("HELIX_A2A_USE_MNNVL", "auto").strip().lower()
+    if v in _FALSE:
+        return "0"
+    if v in _TRUE:
+        return "1"
+    return "auto"
+
+
+def backend() -> str:
+    """``HELIX_A2A_BACKEND``: ``nccl`` (default) or ``native`` for the vLLM hook."""
+    return os.environ.get("HELIX_A2A_BACKEND", "nccl").strip().lower()
+
+
+def timeout_ms() -> int:
+    """``HELIX_A2A_TIMEOUT_MS``: budget of every device-side wait (default 2000 ms)."""
+    try:
+        return max(int(os.environ.get("HELIX_A2A_TIMEOUT_MS", "2000")), 1)
+    except ValueError:
+        return 2000
+
+
+def handle_transport() -> str:
+    """``HELIX_A2A_HANDLE_TRANSPORT``: ``auto`` | ``pidfd`` | ``scm`` | ``cudaipc`` | ``fabric``."""
+    return os.environ.get("HELIX_A2A_HANDLE_TRANSPORT", "auto").strip().lower()
+
+
+def debug() -> bool:
+    return os.environ.get("HELIX_A2A_DEBUG", "0").strip() in _TRUE

@@ -1,0 +1,38 @@
+"""Build / import smoke tests (mirrors the reference's tests/test_build.py:5-26)."""
+import helix_a2a_b200 as helix
+
+
+def test_public_names():
+    for name in ("workspace_size", "allocate_workspace", "init_workspace", "alltoall",
+                 "alltoall_combine", "check_status", "reset_workspace"):
+        assert callable(getattr(helix, name))
+    assert helix.__version__ == "0.1.0"
+
+
+def test_reference_package_name():
+    import helix_a2a
+    for name in ("workspace_size", "allocate_workspace", "init_workspace", "alltoall"):
+        assert callable(getattr(helix_a2a, name))
+    assert helix_a2a.__version__ == "0.1.0"
+
+
+def test_workspace_size_formula():
+    # B200: 148 SMs -> maxCh = 74 for cp <= 8 (values of the reference's formula)
+    assert helix.workspace_size(2) == 77_670_400
+    assert helix.workspace_size(4) == 155_340_800
+    assert helix.workspace_size(8) == 310_681_600
+    assert helix.workspace_size(4) != 16_778_240   # the stale stub value in the reference's docstring
+    for cp in (1, 2, 4, 8, 16):
+        assert helix.workspace_size(cp) > 0
+
+
+def test_extension_builds(native_built):
+    from helix_a2a_b200.ops._ext import ext
+    C = ext()
+    lay = C.layout(8, 148)
+    assert lay["max_channels"] == 148
+    assert lay["row_bytes"] == 310_681_600
+    assert lay["status_offset"] + 256 <= lay["row_bytes"]
+    # MLA message: 1024 B row + 8 B stats -> 9 lines; GQA: 256 + 8 -> 3 lines
+    assert C.wire_bytes(1032) == 9 * 128
+    assert C.wire_bytes(264) == 3 * 128
