@@ -229,7 +229,7 @@ cudaError_t launch_exchange(ExchangeParams p, int channel_override, bool pdl, cu
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
   int na = 0;
-  if (pdl) {
+  if (pdl && !li.cooperative) {  // the single-process emulation launch is cooperative and never chained
     attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;
