@@ -1,0 +1,45 @@
+// Split-KV paged decode attention for B200: host interface.
+//
+// The reference has no attention kernel (vLLM's FlashInfer / FlashAttention backends produce
+// the per-rank partial outputs there, benchmark/sbatch/run_gb200_aiperf_v3.sbatch:95); this
+// library supplies it so that the whole decode step attention -> exchange+combine -> o_proj
+// runs on hand-written sm_100a kernels.  Outputs are exactly what the exchange consumes:
+// normalised partial `o [B, Hq, D]` (bf16) and `lse [B, Hq]` (fp32, base e or base 2).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace helix {
+
+struct GqaDecodeParams {
+  const __nv_bfloat16* q;      // [B, Hq, 128]
+  int64_t q_stride_b, q_stride_h;   // elements
+  CUtensorMap k_map, v_map;    // 4-D (d, token-in-page, kv head, page), box (64, 16, 1, 1), SWIZZLE_128B
+  const int32_t* block_table;  // [B, bt_stride]
+  int64_t bt_stride;
+  const int32_t* seq_lens;     // [B] tokens of the LOCAL KV shard
+  __nv_bfloat16* o;            // [B, Hq, 128]
+  float* lse;                  // [B, Hq]
+  float* part_o;               // scratch [B, Hq, splits, 128] fp32 (only when splits > 1)
+  float* part_lse;             // scratch [B, Hq, splits]
+  int* counters;               // scratch [B * Hkv], zero on entry, zero again on exit
+  int* error_flag;             // set to a helix::Status code when a bounded wait runs out
+  int B, Hq, Hkv, page_size, splits;
+  float scale;
+  int lse_base2;
+  unsigned long long timeout_ns;
+};
+
+// scratch sizes for a launch with `splits` KV splits
+inline size_t gqa_part_o_bytes(int B, int Hq, int splits) { return (size_t)B * Hq * splits * 128 * sizeof(float); }
+inline size_t gqa_part_lse_bytes(int B, int Hq, int splits) { return (size_t)B * Hq * splits * sizeof(float); }
+
+// number of KV splits that fills the device for this batch (>= 1)
+int gqa_pick_splits(int B, int Hkv, int max_seq_len, int sm_count);
+
+cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t stream);
+
+}  // namespace helix

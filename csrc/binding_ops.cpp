@@ -1,7 +1,221 @@
-// Torch bindings of the compute kernels (decode attention, o_proj GEMM, fused paths).
+// Torch bindings of the compute kernels (decode attention, o_proj GEMM).
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
-void register_compute_ops(torch::Library& m) { (void)m; }
-void bind_compute(pybind11::module_& m) { (void)m; }
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "attention.h"
+#include "exchange.h"
+#include "oproj.h"
+#include "tensor_map.h"
+
+namespace {
+
+unsigned long long env_timeout_ns() {
+  const char* v = std::getenv("HELIX_A2A_TIMEOUT_MS");
+  int ms = (v && *v) ? std::atoi(v) : 2000;
+  if (ms < 1) ms = 1;
+  return (unsigned long long)ms * 1000000ull;
+}
+bool env_pdl() {
+  const char* v = std::getenv("HELIX_A2A_ENABLE_PDL");
+  return v && std::string(v) == "1";
+}
+
+// Per-device scratch owned by the library: error flag, counters, split partials.  Grown on demand,
+// never shrunk; all kernels that use it leave counters at zero.
+struct Scratch {
+  torch::Tensor error_flag;    // int32 [1]
+  torch::Tensor counters;      // int32 [N]
+  torch::Tensor part_a, part_b;  // float32 pools
+};
+std::mutex g_mu;
+std::map<int, Scratch> g_scratch;
+
+Scratch& scratch_for(const torch::Device& dev, int64_t counters, int64_t part_a_floats, int64_t part_b_floats) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  Scratch& s = g_scratch[dev.index()];
+  auto iopt = torch::TensorOptions().dtype(torch::kInt32).device(dev);
+  auto fopt = torch::TensorOptions().dtype(torch::kFloat32).device(dev);
+  if (!s.error_flag.defined()) s.error_flag = torch::zeros({1}, iopt);
+  if (!s.counters.defined() || s.counters.numel() < counters) s.counters = torch::zeros({std::max<int64_t>(counters, 4096)}, iopt);
+  if (!s.part_a.defined() || s.part_a.numel() < part_a_floats) s.part_a = torch::empty({std::max<int64_t>(part_a_floats, 1)}, fopt);
+  if (!s.part_b.defined() || s.part_b.numel() < part_b_floats) s.part_b = torch::empty({std::max<int64_t>(part_b_floats, 1)}, fopt);
+  return s;
+}
+
+void check_cuda(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, "helix: ", what, " failed: ", cudaGetErrorString(e));
+}
+
+// ---- tensor-map cache --------------------------------------------------------------------------
+using MapKey = std::tuple<const void*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int>;
+std::map<MapKey, CUtensorMap> g_maps;
+
+CUtensorMap kv_map(const torch::Tensor& cache, bool hnd) {
+  // cache: [pages, Hkv, page, D] (hnd) or [pages, page, Hkv, D]
+  const int64_t pages = cache.size(0), D = cache.size(3);
+  const int64_t Hkv = hnd ? cache.size(1) : cache.size(2), page = hnd ? cache.size(2) : cache.size(1);
+  const int64_t s_page = cache.stride(0), s_head = hnd ? cache.stride(1) : cache.stride(2),
+                s_tok = hnd ? cache.stride(2) : cache.stride(1);
+  MapKey key{cache.data_ptr(), pages, Hkv, page, D, s_page, s_head, s_tok, 1};
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) return it->second;
+  CUtensorMap m;
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)page, (uint64_t)Hkv, (uint64_t)pages};
+  uint64_t strides[3] = {(uint64_t)s_tok * 2, (uint64_t)s_head * 2, (uint64_t)s_page * 2};
+  uint32_t box[4] = {64, 16, 1, 1};
+  const char* err = nullptr;
+  TORCH_CHECK(helix::encode_tensor_map(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, cache.data_ptr(), dims, strides, box,
+                                       helix::TmaSwizzle::k128B, &err),
+              "helix: KV cache tensor map: ", err ? err : "?");
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps[key] = m;
+  return m;
+}
+
+CUtensorMap mat_map(const torch::Tensor& t, int64_t box_rows) {
+  // t: [rows, K] bf16, last dim contiguous
+  MapKey key{t.data_ptr(), t.size(0), t.size(1), t.stride(0), box_rows, 0, 0, 0, 2};
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) return it->second;
+  CUtensorMap m;
+  uint64_t dims[2] = {(uint64_t)t.size(1), (uint64_t)t.size(0)};
+  uint64_t strides[1] = {(uint64_t)t.stride(0) * 2};
+  uint32_t box[2] = {64, (uint32_t)box_rows};
+  const char* err = nullptr;
+  TORCH_CHECK(helix::encode_tensor_map(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, t.data_ptr(), dims, strides, box,
+                                       helix::TmaSwizzle::k128B, &err),
+              "helix: matrix tensor map: ", err ? err : "?");
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps[key] = m;
+  return m;
+}
+
+// ---- GQA paged decode attention -----------------------------------------------------------------
+std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tensor k_cache, torch::Tensor v_cache,
+                                                    torch::Tensor block_table, torch::Tensor seq_lens, double scale,
+                                                    bool lse_base2, bool hnd, int64_t splits, int64_t max_seq_len) {
+  TORCH_CHECK(q.is_cuda() && k_cache.is_cuda() && v_cache.is_cuda() && block_table.is_cuda() && seq_lens.is_cuda(),
+              "all inputs must be on CUDA");
+  TORCH_CHECK(q.scalar_type() == at::ScalarType::BFloat16 && k_cache.scalar_type() == at::ScalarType::BFloat16 &&
+                  v_cache.scalar_type() == at::ScalarType::BFloat16,
+              "q / k_cache / v_cache must be bfloat16");
+  TORCH_CHECK(block_table.scalar_type() == at::ScalarType::Int && seq_lens.scalar_type() == at::ScalarType::Int,
+              "block_table / seq_lens must be int32");
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.stride(2) == 1, "q must be [B, Hq, 128]");
+  TORCH_CHECK(k_cache.dim() == 4 && v_cache.dim() == 4 && k_cache.size(3) == 128 && k_cache.stride(3) == 1 &&
+                  v_cache.stride(3) == 1 && k_cache.sizes() == v_cache.sizes(),
+              "caches must be 4-D with head_dim 128 innermost");
+  TORCH_CHECK(block_table.dim() == 2 && block_table.stride(1) == 1 && block_table.size(0) == q.size(0));
+  TORCH_CHECK(seq_lens.dim() == 1 && seq_lens.size(0) == q.size(0) && seq_lens.is_contiguous());
+  const int B = (int)q.size(0), Hq = (int)q.size(1);
+  const int Hkv = (int)(hnd ? k_cache.size(1) : k_cache.size(2));
+  const int page = (int)(hnd ? k_cache.size(2) : k_cache.size(1));
+  TORCH_CHECK(Hq % Hkv == 0 && Hq / Hkv <= 8, "query heads per KV head must be <= 8");
+  TORCH_CHECK(page % 16 == 0, "page size must be a multiple of 16");
+  c10::cuda::CUDAGuard guard(q.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+
+  int sp = (int)splits;
+  if (sp <= 0) sp = helix::gqa_pick_splits(B, Hkv, (int)std::max<int64_t>(max_seq_len, 1), helix::device_sm_count());
+  torch::Tensor o = torch::empty({B, Hq, 128}, q.options());
+  torch::Tensor lse = torch::empty({B, Hq}, q.options().dtype(torch::kFloat32));
+  if (B == 0) return std::make_tuple(o, lse);
+  Scratch& sc = scratch_for(q.device(), (int64_t)B * Hkv + 1024, sp > 1 ? (int64_t)B * Hq * sp * 128 : 0,
+                            sp > 1 ? (int64_t)B * Hq * sp : 0);
+  helix::GqaDecodeParams p{};
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q.data_ptr());
+  p.q_stride_b = q.stride(0);
+  p.q_stride_h = q.stride(1);
+  p.k_map = kv_map(k_cache, hnd);
+  p.v_map = kv_map(v_cache, hnd);
+  p.block_table = block_table.data_ptr<int32_t>();
+  p.bt_stride = block_table.stride(0);
+  p.seq_lens = seq_lens.data_ptr<int32_t>();
+  p.o = reinterpret_cast<__nv_bfloat16*>(o.data_ptr());
+  p.lse = lse.data_ptr<float>();
+  p.part_o = sc.part_a.data_ptr<float>();
+  p.part_lse = sc.part_b.data_ptr<float>();
+  p.counters = sc.counters.data_ptr<int32_t>();
+  p.error_flag = sc.error_flag.data_ptr<int32_t>();
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page; p.splits = sp;
+  p.scale = (float)scale;
+  p.lse_base2 = lse_base2 ? 1 : 0;
+  p.timeout_ns = env_timeout_ns();
+  check_cuda(helix::launch_gqa_decode(p, env_pdl(), stream), "gqa decode launch");
+  return std::make_tuple(o, lse);
+}
+
+// ---- o_proj ----------------------------------------------------------------------------------------
+torch::Tensor oproj(torch::Tensor x, torch::Tensor w, int64_t splits) {
+  TORCH_CHECK(x.is_cuda() && w.is_cuda(), "inputs must be on CUDA");
+  TORCH_CHECK(x.scalar_type() == at::ScalarType::BFloat16 && w.scalar_type() == at::ScalarType::BFloat16,
+              "x and w must be bfloat16");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1), "x [tokens, K], w [hidden, K]");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1, "innermost dimension must be contiguous");
+  TORCH_CHECK(w.size(0) % 128 == 0 && w.size(1) % 64 == 0, "hidden must be a multiple of 128 and K of 64");
+  TORCH_CHECK((x.stride(0) * 2) % 16 == 0 && (w.stride(0) * 2) % 16 == 0, "row strides must be multiples of 16 bytes");
+  const int tokens = (int)x.size(0), hidden = (int)w.size(0), K = (int)w.size(1);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  torch::Tensor y = torch::empty({tokens, hidden}, x.options());
+  if (tokens == 0) return y;
+  // more than 256 tokens: run the kernel per 256-token slice (decode batches are smaller)
+  for (int t0 = 0; t0 < tokens; t0 += 256) {
+    const int nt = std::min(256, tokens - t0);
+    torch::Tensor xs = x.narrow(0, t0, nt);
+    const int n_pad = (nt + 15) / 16 * 16;
+    int sp = (int)splits;
+    if (sp <= 0) sp = helix::oproj_pick_splits(hidden, K, helix::device_sm_count());
+    Scratch& sc = scratch_for(x.device(), hidden / 128 + 1024, sp > 1 ? (int64_t)helix::oproj_partial_bytes(hidden, sp, n_pad) / 4 : 0, 0);
+    helix::OprojParams p{};
+    p.w_map = mat_map(w, 128);
+    p.x_map = mat_map(xs, n_pad);
+    p.y = reinterpret_cast<__nv_bfloat16*>(y.data_ptr()) + (int64_t)t0 * y.stride(0);
+    p.y_stride = y.stride(0);
+    p.partial = sc.part_a.data_ptr<float>();
+    // o_proj counters live after the attention counters
+    p.counters = sc.counters.data_ptr<int32_t>() + (sc.counters.numel() - hidden / 128);
+    p.error_flag = sc.error_flag.data_ptr<int32_t>();
+    p.tokens = nt; p.n_pad = n_pad; p.hidden = hidden; p.K = K; p.splits = sp;
+    p.stages = helix::oproj_pick_stages(n_pad);
+    p.timeout_ns = env_timeout_ns();
+    check_cuda(helix::launch_oproj(p, env_pdl(), stream), "o_proj launch");
+  }
+  return y;
+}
+
+int64_t read_error_flag(torch::Tensor like) {
+  Scratch& sc = scratch_for(like.device(), 1, 0, 0);
+  return sc.error_flag.item<int>();
+}
+
+void clear_error_flag(torch::Tensor like) {
+  Scratch& sc = scratch_for(like.device(), 1, 0, 0);
+  sc.error_flag.zero_();
+  sc.counters.zero_();
+}
+
+}  // namespace
+
+void register_compute_ops(torch::Library& m) {
+  m.def(
+      "gqa_decode(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_table, Tensor seq_lens, float scale, bool "
+      "lse_base2, bool hnd, int splits, int max_seq_len) -> (Tensor, Tensor)",
+      &gqa_decode);
+  m.def("oproj(Tensor x, Tensor w, int splits) -> Tensor", &oproj);
+  m.def("read_error_flag(Tensor like) -> int", &read_error_flag);
+  m.def("clear_error_flag(Tensor like) -> ()", &clear_error_flag);
+}
+
+void bind_compute(pybind11::module_& m) {
+  m.def("gqa_pick_splits", &helix::gqa_pick_splits);
+  m.def("oproj_pick_splits", &helix::oproj_pick_splits);
+}

@@ -1,0 +1,35 @@
+// o_proj GEMM for decode on B200: y[tokens, hidden] = x[tokens, K] * W[hidden, K]^T  (bf16 in, fp32
+// accumulate in TMEM, bf16 out).  In the reference this layer is vLLM's cuBLAS linear; here it is a
+// hand-written tcgen05 kernel so that it can chain to the exchange by programmatic dependent launch
+// and stream its weights while the exchange is still in flight.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace helix {
+
+struct OprojParams {
+  CUtensorMap w_map;     // 2-D (K, hidden), box (64, 128), SWIZZLE_128B
+  CUtensorMap x_map;     // 2-D (K, tokens), box (64, n_pad), SWIZZLE_128B
+  __nv_bfloat16* y;      // [tokens, hidden]
+  int64_t y_stride;      // elements between token rows
+  float* partial;        // scratch [m_tiles][splits][n_pad][128] fp32 (splits > 1)
+  int* counters;         // scratch [m_tiles], zero on entry and on exit
+  int* error_flag;
+  int tokens, n_pad, hidden, K, splits, stages;
+  unsigned long long timeout_ns;
+};
+
+inline size_t oproj_partial_bytes(int hidden, int splits, int n_pad) {
+  return (size_t)(hidden / 128) * splits * n_pad * 128 * sizeof(float);
+}
+int oproj_pick_splits(int hidden, int K, int sm_count);
+int oproj_pick_stages(int n_pad);
+int oproj_smem_bytes(int n_pad, int stages);
+
+cudaError_t launch_oproj(const OprojParams& p, bool pdl, cudaStream_t stream);
+
+}  // namespace helix

@@ -1,0 +1,241 @@
+// Decode o_proj GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulator in TMEM).
+//
+// Decode batches are small (1..256 tokens) while `hidden` is large, so the product is computed
+// transposed ("swap-AB"): the 128-row UMMA M dimension walks `hidden` (rows of W), the token count
+// is the UMMA N dimension (padded to a multiple of 16) and D[128, n_pad] fp32 lives in TMEM.  The
+// kernel is bound by streaming W once from HBM:
+//   grid (hidden / 128, splits); each CTA owns one 128-row slab of W and 1/splits of K;
+//   warp 0 (one lane) feeds a ring of shared-memory stages with TMA tiled loads (128-byte swizzle,
+//     W tile [128 x 64] + x tile [n_pad x 64] per stage, no cluster broadcast);
+//   warp 1 (one lane) issues four K=16 UMMAs per stage and releases the stage with
+//     tcgen05.commit; after the last stage it commits to the accumulator barrier;
+//   all four warps then read the accumulator with tcgen05.ld (warp w owns TMEM lanes 32w..32w+31)
+//     and write y (bf16) or, with split-K, park an fp32 partial in scratch memory where the last
+//     CTA of the slab sums the splits.
+// With programmatic dependent launch the W tiles of the first stages are requested BEFORE the
+// grid-dependency wait: only the activations depend on the preceding exchange kernel, so the
+// weight stream overlaps it.  All mbarrier waits are bounded.
+#include "oproj.h"
+
+#include <algorithm>
+
+#include "helix_common.cuh"
+#include "sm100.cuh"
+
+namespace helix {
+namespace {
+
+using namespace sm100;
+
+constexpr int kBM = 128;   // rows of W per CTA (UMMA M)
+constexpr int kBK = 64;    // K per stage: one 128-byte swizzle atom of bf16
+constexpr int kMaxStages = 12;
+constexpr int kThreads = 128;
+
+__device__ __forceinline__ void fail(const OprojParams& p, int* s_abort) {
+  atomicCAS(p.error_flag, 0, (int)kTimeoutMbarrier);
+  *reinterpret_cast<volatile int*>(s_abort) = 1;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) oproj_kernel(const __grid_constant__ OprojParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort, s_last;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tile = blockIdx.x, split = blockIdx.y;
+  const int stages = p.stages;
+  const uint32_t a_bytes = kBM * kBK * 2, b_bytes = (uint32_t)p.n_pad * kBK * 2;
+  const uint32_t stage_bytes = a_bytes + b_bytes;          // multiples of 1024
+  const int kb_total = p.K / kBK;
+  const int kb_per = (kb_total + p.splits - 1) / p.splits;
+  const int kb0 = split * kb_per;
+  const int nkb = max(0, min(kb_total, kb0 + kb_per) - kb0);
+  uint32_t tmem_cols = 32;
+  while ((int)tmem_cols < p.n_pad) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    mbar_fence_init();
+    s_abort = 0;
+    tma_prefetch_desc(&p.w_map);
+    tma_prefetch_desc(&p.x_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_d = tmem_slot;
+  const unsigned long long deadline = now_ns() + p.timeout_ns;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- producer ----------------
+    // weights first: they do not depend on the kernel before us
+    const int pre = min(stages, nkb);
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(&full_bar[i], stage_bytes);
+      tma_load_2d(smem + (size_t)i * stage_bytes, &p.w_map, &full_bar[i], (kb0 + i) * kBK, m_tile * kBM);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int i = 0; i < pre; ++i)
+      tma_load_2d(smem + (size_t)i * stage_bytes + a_bytes, &p.x_map, &full_bar[i], (kb0 + i) * kBK, 0);
+    for (int i = pre; i < nkb; ++i) {
+      const int s = i % stages;
+      if (!mbar_wait(&empty_bar[s], (uint32_t)(((i / stages) - 1) & 1), deadline)) {
+        fail(p, &s_abort);
+        break;
+      }
+      mbar_expect_tx(&full_bar[s], stage_bytes);
+      tma_load_2d(smem + (size_t)s * stage_bytes, &p.w_map, &full_bar[s], (kb0 + i) * kBK, m_tile * kBM);
+      tma_load_2d(smem + (size_t)s * stage_bytes + a_bytes, &p.x_map, &full_bar[s], (kb0 + i) * kBK, 0);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer ----------------
+    const uint32_t idesc = umma_idesc_bf16(kBM, p.n_pad);
+    bool ok = true;
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int s = i % stages;
+      if (!mbar_wait(&full_bar[s], (uint32_t)((i / stages) & 1), deadline)) {
+        fail(p, &s_abort);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
+      const uint32_t b_addr = a_addr + a_bytes;
+#pragma unroll
+      for (int k = 0; k < kBK / 16; ++k) {
+        umma_bf16(tmem_d, umma_desc_k_sw128(a_addr + k * 32), umma_desc_k_sw128(b_addr + k * 32), idesc,
+                  (i | k) != 0);
+      }
+      umma_commit(&empty_bar[s]);          // stage reusable once these MMAs have read it
+    }
+    if (ok) umma_commit(&acc_bar);         // accumulator complete
+  }
+  if (warp >= 0) {
+    // ---------------- epilogue (all four warps) ----------------
+    __syncwarp();
+    bool ok = true;
+    if (nkb > 0) {
+      // only lane 0 polls, then the result is broadcast: a failed wait must not diverge the warp
+      int good = 1;
+      if (lane == 0) {
+        unsigned spins = 0;
+        while (!mbar_try_wait(&acc_bar, 0)) {
+          if ((++spins & 63u) == 0u) {
+            if (*reinterpret_cast<volatile int*>(&s_abort) || now_ns() > deadline) {
+              good = 0;
+              break;
+            }
+          }
+        }
+      }
+      good = __shfl_sync(0xffffffffu, good, 0);
+      ok = good != 0;
+      if (!ok && lane == 0) fail(p, &s_abort);
+    }
+    tc_fence_after_sync();
+    const int row = warp * 32 + lane;                 // TMEM lane == row of the W slab
+    const int hcol = m_tile * kBM + row;
+    float* part = p.partial + ((size_t)(m_tile * p.splits + split) * p.n_pad) * kBM;
+    if (ok) {
+      for (int c0 = 0; c0 < p.n_pad; c0 += 16) {
+        uint32_t v[16];
+        if (nkb > 0) {
+          tmem_ld_32x32b_x16(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int tok = c0 + j;
+          if (p.splits == 1) {
+            if (tok < p.tokens) p.y[(int64_t)tok * p.y_stride + hcol] = __float2bfloat16(__uint_as_float(v[j]));
+          } else {
+            part[(size_t)tok * kBM + row] = __uint_as_float(v[j]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_d, tmem_cols);
+  if (p.splits == 1) return;
+
+  // ---------------- split-K: the last CTA of this slab sums the partials ----------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(&p.counters[m_tile], 1);
+    s_last = (prev == p.splits - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int row = threadIdx.x;
+  const float* base = p.partial + (size_t)m_tile * p.splits * p.n_pad * kBM;
+  for (int tok = 0; tok < p.tokens; ++tok) {
+    float acc = 0.f;
+    for (int s = 0; s < p.splits; ++s) acc += __ldcg(base + ((size_t)s * p.n_pad + tok) * kBM + row);
+    p.y[(int64_t)tok * p.y_stride + m_tile * kBM + row] = __float2bfloat16(acc);
+  }
+  if (threadIdx.x == 0) p.counters[m_tile] = 0;
+}
+
+}  // namespace
+
+int oproj_pick_splits(int hidden, int K, int sm_count) {
+  const int m_tiles = hidden / kBM;
+  int splits = std::max(1, sm_count / std::max(m_tiles, 1));
+  const int kb_total = K / kBK;
+  while (splits > 1 && kb_total / splits < 4) --splits;     // keep a few k-blocks per CTA
+  return std::min(splits, 8);
+}
+
+int oproj_smem_bytes(int n_pad, int stages) { return stages * (kBM * kBK * 2 + n_pad * kBK * 2) + 1024; }
+
+int oproj_pick_stages(int n_pad) {
+  const int stage = kBM * kBK * 2 + n_pad * kBK * 2;
+  int s = (200 * 1024) / stage;
+  return std::max(2, std::min(s, kMaxStages));
+}
+
+cudaError_t launch_oproj(const OprojParams& p, bool pdl, cudaStream_t stream) {
+  if (p.tokens <= 0) return cudaSuccess;
+  if (p.hidden % kBM != 0 || p.K % kBK != 0 || p.n_pad % 16 != 0 || p.n_pad < 16 || p.n_pad > 256 ||
+      p.tokens > p.n_pad || p.stages < 2 || p.stages > kMaxStages || p.splits < 1)
+    return cudaErrorInvalidValue;
+  const int smem = oproj_smem_bytes(p.n_pad, p.stages);
+  cudaError_t e = cudaFuncSetAttribute(oproj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(p.hidden / kBM, p.splits, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  int na = 0;
+  if (pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, oproj_kernel, p);
+}
+
+}  // namespace helix

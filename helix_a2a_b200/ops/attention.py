@@ -1,0 +1,39 @@
+"""Split-KV paged decode attention (per-rank partial output + LSE).
+
+``gqa_decode`` runs the hand-written sm_100a kernel (``csrc/decode_attn_gqa.cu``); on CPU
+tensors it falls back to the fp32 oracle so that the model code runs without a GPU.  In the
+reference this step belongs to vLLM's attention backends
+(``benchmark/sbatch/run_gb200_aiperf_v3.sbatch:95``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import reference_math as rm
+
+
+def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+               seq_lens: torch.Tensor, *, scale: Optional[float] = None, lse_base2: bool = False,
+               layout: str = "HND", splits: int = 0, max_seq_len: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Decode attention of ``q [B, Hq, 128]`` over each sequence's local KV pages.
+
+    ``k_cache`` / ``v_cache``: ``[pages, Hkv, page, 128]`` (``layout="HND"``) or
+    ``[pages, page, Hkv, 128]`` (``"NHD"``), bf16.  ``block_table [B, max_pages]`` int32,
+    ``seq_lens [B]`` int32 (tokens of the LOCAL shard).  Returns ``o [B, Hq, 128]`` (bf16,
+    normalised) and ``lse [B, Hq]`` (fp32; natural log, or base 2 with ``lse_base2``).
+    ``splits=0`` lets the library pick the number of KV splits from ``max_seq_len``.
+    """
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if not q.is_cuda:
+        kc = k_cache if layout == "HND" else k_cache.permute(0, 2, 1, 3)
+        vc = v_cache if layout == "HND" else v_cache.permute(0, 2, 1, 3)
+        o, lse = rm.paged_decode_attention_reference(q, kc, vc, block_table, seq_lens, scale, lse_base2)
+        return o.to(q.dtype), lse
+    from ._ext import ops
+    if max_seq_len <= 0:
+        max_seq_len = block_table.shape[1] * (k_cache.shape[2] if layout == "HND" else k_cache.shape[1])
+    return ops().gqa_decode(q, k_cache, v_cache, block_table, seq_lens, float(scale), lse_base2,
+                            layout == "HND", splits, max_seq_len)

@@ -1,0 +1,83 @@
+"""Numerics of the decode attention and o_proj kernels against plain PyTorch fp32 references."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def built(native_built):
+    from helix_a2a_b200.ops._ext import ext
+    ext()
+    return True
+
+
+def _paged_case(B, Hq, Hkv, seq_lens, page=16, layout="HND", seed=0):
+    torch.manual_seed(seed)
+    D = 128
+    max_blocks = max((s + page - 1) // page for s in seq_lens)
+    n_pages = B * max_blocks + 3
+    perm = torch.randperm(n_pages)[:B * max_blocks].view(B, max_blocks).int()
+    shape = (n_pages, Hkv, page, D) if layout == "HND" else (n_pages, page, Hkv, D)
+    kc = torch.randn(shape, device="cuda").bfloat16()
+    vc = torch.randn(shape, device="cuda").bfloat16()
+    q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+    return q, kc, vc, perm.cuda(), torch.tensor(seq_lens, dtype=torch.int32, device="cuda")
+
+
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+@pytest.mark.parametrize("seq_lens,splits", [([5], 1), ([16, 17, 300], 1), ([1000, 37, 512, 2048], 3),
+                                             ([4096, 4000], 0), ([129] * 5, 4)])
+def test_gqa_decode_matches_fp32_reference(built, layout, seq_lens, splits):
+    from helix_a2a_b200.ops import attention, reference_math as rm
+    from helix_a2a_b200.ops.oproj import check_compute_status
+    B, Hq, Hkv = len(seq_lens), 64, 8
+    q, kc, vc, bt, sl = _paged_case(B, Hq, Hkv, seq_lens, layout=layout, seed=len(seq_lens))
+    o, lse = attention.gqa_decode(q, kc, vc, bt, sl, layout=layout, splits=splits, max_seq_len=max(seq_lens))
+    torch.cuda.synchronize()
+    check_compute_status(q)
+    kr = kc if layout == "HND" else kc.permute(0, 2, 1, 3)
+    vr = vc if layout == "HND" else vc.permute(0, 2, 1, 3)
+    o_ref, lse_ref = rm.paged_decode_attention_reference(q.float(), kr.float(), vr.float(), bt, sl, 1 / math.sqrt(128))
+    assert (o.float() - o_ref).abs().max() < 2e-2
+    assert (lse - lse_ref).abs().max() < 2e-3
+
+
+def test_gqa_decode_small_group_base2_and_empty_sequence(built):
+    from helix_a2a_b200.ops import attention, reference_math as rm
+    seq_lens = [0, 40, 16]
+    q, kc, vc, bt, sl = _paged_case(3, 8, 2, seq_lens, page=32, seed=7)       # group of 4, page 32
+    o, lse = attention.gqa_decode(q, kc, vc, bt, sl, lse_base2=True, splits=2)
+    o_ref, lse_ref = rm.paged_decode_attention_reference(q.float(), kc.float(), vc.float(), bt, sl,
+                                                         1 / math.sqrt(128), base2=True)
+    assert (o.float() - o_ref).abs().max() < 2e-2
+    assert (o[0] == 0).all() and (lse[0] == float("-inf")).all()
+    assert (lse[1:] - lse_ref[1:]).abs().max() < 3e-3
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 17, 64, 200, 300])
+@pytest.mark.parametrize("hidden,K,splits", [(8192, 1024, 0), (1024, 8192, 1), (512, 256, 2), (8192, 8192, 0)])
+def test_oproj_matches_fp32_matmul(built, tokens, hidden, K, splits):
+    from helix_a2a_b200.ops.oproj import oproj, check_compute_status
+    torch.manual_seed(tokens + hidden)
+    x = torch.randn(tokens, K, device="cuda").bfloat16()
+    w = (torch.randn(hidden, K, device="cuda") * 0.02).bfloat16()
+    y = oproj(x, w, splits=splits)
+    torch.cuda.synchronize()
+    check_compute_status(x)
+    ref = x.float() @ w.float().t()
+    err = (y.float() - ref).abs().max().item()
+    assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
+
+
+def test_oproj_on_column_slice_of_full_weight(built):
+    """Each CP rank multiplies by its K-slice of W_o: a strided view, no copy."""
+    from helix_a2a_b200.ops.oproj import oproj
+    w_full = (torch.randn(1024, 4096, device="cuda") * 0.02).bfloat16()
+    x = torch.randn(9, 1024, device="cuda").bfloat16()
+    w_slice = w_full[:, 1024:2048]
+    y = oproj(x, w_slice)
+    ref = x.float() @ w_slice.float().t()
+    assert (y.float() - ref).abs().max() < 2e-2
