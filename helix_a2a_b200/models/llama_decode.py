@@ -1,0 +1,163 @@
+"""Llama-3-70B-architecture decode stack under Helix context parallelism.
+
+One decode step of the attention block of every layer on one CP rank::
+
+    split-KV paged attention over the LOCAL KV shard   ->  (o [B, Hq, D], lse [B, Hq])
+    Helix exchange + LSE combine (head scatter)        ->  x [B, Hq/N, D]
+    o_proj with this rank's K-slice of W_o             ->  y [B, hidden]   (partial sum over ranks)
+
+The KV cache of every sequence is split evenly over the ``cp_size`` ranks; each rank holds all KV
+heads of its shard.  Weights are random-init (N(0, 0.02)), KV ~ N(0, 1): there is no checkpoint
+loading here, the stack exists to drive and measure the kernels on the shapes of a real model.
+The reference leaves all of this to vLLM (``benchmark/sbatch/run_gb200_aiperf_v3.sbatch:284-305``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import api
+from ..ops import attention, oproj as oproj_mod
+
+
+@dataclass
+class LlamaDecodeConfig:
+    n_layers: int = 80
+    n_q_heads: int = 64
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    hidden: int = 8192
+    page_size: int = 16
+    dtype: torch.dtype = torch.bfloat16
+
+    @staticmethod
+    def llama3_70b(**kw) -> "LlamaDecodeConfig":
+        return LlamaDecodeConfig(**kw)
+
+    @staticmethod
+    def tiny(**kw) -> "LlamaDecodeConfig":
+        base = dict(n_layers=2, n_q_heads=16, n_kv_heads=2, head_dim=128, hidden=256)
+        base.update(kw)
+        return LlamaDecodeConfig(**base)
+
+
+class HelixDecodeStack:
+    """KV cache shard, o_proj slices and workspace of one CP rank, plus the decode step."""
+
+    def __init__(self, cfg: LlamaDecodeConfig, *, batch: int, local_ctx: int, cp_size: int = 1, cp_rank: int = 0,
+                 group: Optional[dist.ProcessGroup] = None, device="cuda", seed: int = 0,
+                 workspace: Optional[torch.Tensor] = None, kv_std: float = 1.0):
+        assert cfg.n_q_heads % cp_size == 0, "query heads must divide evenly over the CP ranks"
+        self.cfg, self.batch, self.local_ctx = cfg, batch, local_ctx
+        self.cp_size, self.cp_rank, self.group = cp_size, cp_rank, group
+        self.device = torch.device(device)
+        self.heads_local = cfg.n_q_heads // cp_size
+        self.k_local = self.heads_local * cfg.head_dim
+        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(seed * 1000 + cp_rank)
+        pages_per_seq = (local_ctx + cfg.page_size - 1) // cfg.page_size
+        self.n_pages = batch * pages_per_seq
+        # pages of a sequence are scattered over the pool, as a paged allocator would leave them
+        perm = torch.randperm(self.n_pages, generator=torch.Generator().manual_seed(seed)).int()
+        self.block_table = perm.view(batch, pages_per_seq).to(self.device)
+        self.seq_lens = torch.full((batch,), local_ctx, dtype=torch.int32, device=self.device)
+        shape = (self.n_pages, cfg.n_kv_heads, cfg.page_size, cfg.head_dim)
+        self.k_cache: List[torch.Tensor] = []
+        self.v_cache: List[torch.Tensor] = []
+        self.w_o: List[torch.Tensor] = []
+        for _ in range(cfg.n_layers):
+            k = torch.empty(shape, dtype=cfg.dtype, device=self.device).normal_(0, kv_std, generator=gen)
+            v = torch.empty(shape, dtype=cfg.dtype, device=self.device).normal_(0, kv_std, generator=gen)
+            w = torch.empty(cfg.hidden, self.k_local, dtype=cfg.dtype, device=self.device).normal_(0, 0.02, generator=gen)
+            self.k_cache.append(k)
+            self.v_cache.append(v)
+            self.w_o.append(w)
+        if workspace is not None:
+            self.workspace = workspace
+        elif cp_size > 1:
+            self.workspace = api.allocate_workspace(cp_size, cp_rank, device=device if self.device.type == "cpu" else "cuda",
+                                                    mnnvl=True, cpu_group=group)
+            api.init_workspace(self.workspace, cp_rank, cp_size)
+            dist.barrier(group=group)
+        else:
+            self.workspace = None
+        self._graph = None
+        self._static_q = None
+        self._static_y = None
+
+    # ---- one layer / one step --------------------------------------------------------------------
+    def layer(self, l: int, q: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        o, lse = attention.gqa_decode(q, self.k_cache[l], self.v_cache[l], self.block_table, self.seq_lens,
+                                      scale=self.scale, max_seq_len=self.local_ctx)
+        if self.cp_size > 1:
+            x = api.alltoall_combine(o, lse, self.workspace, self.cp_rank, self.cp_size)
+        else:
+            x = o
+        return oproj_mod.oproj(x.reshape(self.batch, self.k_local), self.w_o[l])
+
+    def decode_step(self, q_all: torch.Tensor) -> torch.Tensor:
+        """``q_all [L, B, Hq, D]`` on the device -> ``y [L, B, hidden]`` (this rank's partial sums)."""
+        ys = [self.layer(l, q_all[l]) for l in range(self.cfg.n_layers)]
+        return torch.stack(ys)
+
+    def _step_last(self, q_all: torch.Tensor) -> torch.Tensor:
+        y = None
+        for l in range(self.cfg.n_layers):
+            y = self.layer(l, q_all[l])
+        return y
+
+    # ---- end-to-end call: pinned host input -> host output ---------------------------------------
+    def capture(self, q_example: torch.Tensor) -> None:
+        """Capture the whole step in a CUDA graph (call after at least one eager warm-up step)."""
+        self._static_q = torch.empty_like(q_example, device=self.device)
+        self._static_q.copy_(q_example)
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self._step_last(self._static_q)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                self._static_y = self._step_last(self._static_q)
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        self._graph = g
+
+    def decode_step_device(self, q_dev: torch.Tensor) -> torch.Tensor:
+        """Step on device-resident ``q``; returns the last layer's ``y`` (``[B, hidden]``)."""
+        if self._graph is not None:
+            self._static_q.copy_(q_dev, non_blocking=True)
+            self._graph.replay()
+            return self._static_y
+        return self._step_last(q_dev)
+
+    def decode_step_host(self, q_pinned: torch.Tensor, out_pinned: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Public end-to-end step: copies ``q`` from pinned host memory, runs every layer, copies
+        the result (``[B, hidden]``) back to the host and waits for it."""
+        q_dev = self._static_q if self._graph is not None else torch.empty_like(q_pinned, device=self.device)
+        q_dev.copy_(q_pinned, non_blocking=True)
+        if self._graph is not None:
+            self._graph.replay()
+            y = self._static_y
+        else:
+            y = self._step_last(q_dev)
+        if out_pinned is None:
+            out_pinned = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
+        out_pinned.copy_(y, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return out_pinned
+
+    # ---- accounting ------------------------------------------------------------------------------
+    def kernels_per_step(self) -> int:
+        return self.cfg.n_layers * (3 if self.cp_size > 1 else 2)
+
+    def h2d_bytes_per_step(self) -> int:
+        c = self.cfg
+        return c.n_layers * self.batch * c.n_q_heads * c.head_dim * 2
+
+    def d2h_bytes_per_step(self) -> int:
+        return self.batch * self.cfg.hidden * 2
