@@ -1,0 +1,51 @@
+#!/usr/bin/env python
+"""Small fixed cases for profiler captures (one kernel, a few launches, ~1 GB on the device).
+
+    python benchmarks/profile_case.py attn      # GQA decode, B=8, 16K tokens per sequence (537 MB of KV)
+    python benchmarks/profile_case.py oproj     # o_proj, 8 tokens, K=8192, hidden 8192 (134 MB of W)
+    python benchmarks/profile_case.py exchange  # fused exchange+combine, 4 ranks played by one launch
+"""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import torch  # noqa: E402
+
+
+def main():
+    which = sys.argv[1] if len(sys.argv) > 1 else "attn"
+    launches = 3
+    if which == "attn":
+        from helix_a2a_b200.ops import attention
+        B, ctx, Hq, Hkv, D, page = 8, 16384, 64, 8, 128, 16
+        pages = B * ctx // page
+        bt = torch.randperm(pages).int().view(B, -1).cuda()
+        sl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        kc = torch.randn(pages, Hkv, page, D, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn(pages, Hkv, page, D, device="cuda", dtype=torch.bfloat16)
+        q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+        for _ in range(launches):
+            attention.gqa_decode(q, kc, vc, bt, sl, max_seq_len=ctx)
+    elif which == "oproj":
+        from helix_a2a_b200.ops.oproj import oproj
+        w = (torch.randn(8192, 8192, device="cuda") * 0.02).bfloat16()
+        x = torch.randn(8, 8192, device="cuda").bfloat16()
+        for _ in range(launches):
+            oproj(x, w)
+    else:
+        import helix_a2a_b200 as helix
+        from helix_a2a_b200.ops._ext import ops
+        cp, B, H, D = 4, 64, 128, 512
+        ws = helix.allocate_workspace(cp, 0)
+        helix.init_workspace_all_rows(ws, cp)
+        outs = torch.randn(cp, B, H, D, device="cuda").bfloat16()
+        lses = torch.randn(cp, B, H, device="cuda")
+        for _ in range(launches):
+            ops().alltoall_combine(outs, lses, ws, 0, cp, 0, False, False, 0, True, 0, 0)
+    torch.cuda.synchronize()
+    print("done", which)
+
+
+if __name__ == "__main__":
+    main()

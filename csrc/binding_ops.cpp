@@ -32,6 +32,7 @@ struct Scratch {
   torch::Tensor error_flag;    // int32 [1]
   torch::Tensor counters;      // int32 [N]
   torch::Tensor part_a, part_b;  // float32 pools
+  torch::Tensor trace;           // int64 [kGqaMaxCtas * 4], only with HELIX_A2A_ATTN_TRACE=1
 };
 std::mutex g_mu;
 std::map<int, Scratch> g_scratch;
@@ -123,13 +124,15 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   c10::cuda::CUDAGuard guard(q.device());
   auto stream = at::cuda::getCurrentCUDAStream();
 
-  int sp = (int)splits;
-  if (sp <= 0) sp = helix::gqa_pick_splits(B, Hkv, (int)std::max<int64_t>(max_seq_len, 1), helix::device_sm_count());
+  // splits > 0 asks for about that many CTAs per (sequence, kv head) pair; 0 lets the library choose
+  int sp = splits > 0 ? (int)std::min<int64_t>((int64_t)B * Hkv * splits, helix::kGqaMaxCtas)
+                      : helix::gqa_pick_ctas(B, Hkv, (int)std::max<int64_t>(max_seq_len, 1), helix::device_sm_count());
+  sp = std::max(sp, 1);
   torch::Tensor o = torch::empty({B, Hq, 128}, q.options());
   torch::Tensor lse = torch::empty({B, Hq}, q.options().dtype(torch::kFloat32));
   if (B == 0) return std::make_tuple(o, lse);
-  Scratch& sc = scratch_for(q.device(), (int64_t)B * Hkv + 1024, sp > 1 ? (int64_t)B * Hq * sp * 128 : 0,
-                            sp > 1 ? (int64_t)B * Hq * sp : 0);
+  Scratch& sc = scratch_for(q.device(), (int64_t)B * Hkv + 1024, (int64_t)helix::gqa_part_o_floats(sp),
+                            (int64_t)helix::gqa_part_lse_floats(sp));
   helix::GqaDecodeParams p{};
   p.q = reinterpret_cast<const __nv_bfloat16*>(q.data_ptr());
   p.q_stride_b = q.stride(0);
@@ -145,10 +148,18 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   p.part_lse = sc.part_b.data_ptr<float>();
   p.counters = sc.counters.data_ptr<int32_t>();
   p.error_flag = sc.error_flag.data_ptr<int32_t>();
-  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page; p.splits = sp;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page; p.ctas = sp;
   p.scale = (float)scale;
   p.lse_base2 = lse_base2 ? 1 : 0;
   p.timeout_ns = env_timeout_ns();
+  p.trace = nullptr;
+  {
+    const char* tr = std::getenv("HELIX_A2A_ATTN_TRACE");
+    if (tr && tr[0] == '1') {
+      if (!sc.trace.defined()) sc.trace = torch::zeros({helix::kGqaMaxCtas * 4}, q.options().dtype(torch::kInt64));
+      p.trace = reinterpret_cast<unsigned long long*>(sc.trace.data_ptr());
+    }
+  }
   check_cuda(helix::launch_gqa_decode(p, env_pdl(), stream), "gqa decode launch");
   return std::make_tuple(o, lse);
 }
@@ -192,6 +203,12 @@ torch::Tensor oproj(torch::Tensor x, torch::Tensor w, int64_t splits) {
   return y;
 }
 
+torch::Tensor attn_trace(torch::Tensor like) {
+  Scratch& sc = scratch_for(like.device(), 1, 0, 0);
+  TORCH_CHECK(sc.trace.defined(), "no trace recorded: set HELIX_A2A_ATTN_TRACE=1");
+  return sc.trace.clone();
+}
+
 int64_t read_error_flag(torch::Tensor like) {
   Scratch& sc = scratch_for(like.device(), 1, 0, 0);
   return sc.error_flag.item<int>();
@@ -212,10 +229,11 @@ void register_compute_ops(torch::Library& m) {
       &gqa_decode);
   m.def("oproj(Tensor x, Tensor w, int splits) -> Tensor", &oproj);
   m.def("read_error_flag(Tensor like) -> int", &read_error_flag);
+  m.def("attn_trace(Tensor like) -> Tensor", &attn_trace);
   m.def("clear_error_flag(Tensor like) -> ()", &clear_error_flag);
 }
 
 void bind_compute(pybind11::module_& m) {
-  m.def("gqa_pick_splits", &helix::gqa_pick_splits);
+  m.def("gqa_pick_ctas", &helix::gqa_pick_ctas);
   m.def("oproj_pick_splits", &helix::oproj_pick_splits);
 }

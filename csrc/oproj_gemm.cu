@@ -187,10 +187,18 @@ __global__ void __launch_bounds__(kThreads, 1) oproj_kernel(const __grid_constan
   __threadfence();
   const int row = threadIdx.x;
   const float* base = p.partial + (size_t)m_tile * p.splits * p.n_pad * kBM;
-  for (int tok = 0; tok < p.tokens; ++tok) {
-    float acc = 0.f;
-    for (int s = 0; s < p.splits; ++s) acc += __ldcg(base + ((size_t)s * p.n_pad + tok) * kBM + row);
-    p.y[(int64_t)tok * p.y_stride + m_tile * kBM + row] = __float2bfloat16(acc);
+  for (int tok0 = 0; tok0 < p.tokens; tok0 += 8) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)   // rows of the partial are padded to n_pad (a multiple of 16): always in bounds
+        acc[j] += __ldcg(base + ((size_t)s * p.n_pad + tok0 + j) * kBM + row);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (tok0 + j < p.tokens) p.y[(int64_t)(tok0 + j) * p.y_stride + m_tile * kBM + row] = __float2bfloat16(acc[j]);
   }
   if (threadIdx.x == 0) p.counters[m_tile] = 0;
 }
@@ -198,10 +206,12 @@ __global__ void __launch_bounds__(kThreads, 1) oproj_kernel(const __grid_constan
 }  // namespace
 
 int oproj_pick_splits(int hidden, int K, int sm_count) {
+  // split K only when one CTA per 128-row slab would leave SMs idle for long: each CTA should still
+  // stream at least 16 k-blocks (256 KB of W)
   const int m_tiles = hidden / kBM;
   int splits = std::max(1, sm_count / std::max(m_tiles, 1));
   const int kb_total = K / kBK;
-  while (splits > 1 && kb_total / splits < 4) --splits;     // keep a few k-blocks per CTA
+  while (splits > 1 && kb_total / splits < 16) --splits;
   return std::min(splits, 8);
 }
 
