@@ -1,0 +1,229 @@
+#!/usr/bin/env python
+"""Exchange (+combine) micro-benchmark: this library against NCCL + torch, DCP AG+RS and the
+reference's own kernel, on the same GPUs, device-timed, max over ranks.
+
+    torchrun --nproc-per-node N benchmarks/exchange_bench.py [--shapes mla,gqa] [--mode graph|eager|both]
+                                                              [--tokens 1,8,32,128,256] [--json out.json]
+
+Paths (all produce the combined ``[B, H/N, D]`` rows of this rank):
+  helix_fused      one kernel: exchange with the LSE combine fused into the receive side
+  helix_exchange   this library's exchange with the reference's contract + torch combine
+  nccl_torch       two NCCL all_to_all_single + torch combine (the baseline build)
+  dcp_ag_rs        all-gather of LSEs, local re-weighting, reduce-scatter of outputs
+  reference        the unmodified reference kernel (baseline/_ref) + its Triton combine, with the
+                   layout copies its vLLM hook performs (patches/dcp_alltoall_helix.py:511-600)
+The protocol follows the reference's micro-benchmark (benchmark/scripts/benchmark_helix_pipeline.py:
+warm-up, CUDA events, eager and CUDA-graph modes); every number is the max over ranks.
+Roofline: bytes that must cross NVLink per rank and direction / 770 GB/s (measured peer copy).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+REF = os.path.join(ROOT, "baseline", "_ref")
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+import helix_a2a_b200 as helix  # noqa: E402
+from helix_a2a_b200.ops import reference_math as rm  # noqa: E402
+
+NVLINK_GBS = 770.0
+
+
+class _Group:
+    def __init__(self, rank, world, device_group, cpu_group):
+        self.rank_in_group, self.world_size = rank, world
+        self.device_group, self.cpu_group = device_group, cpu_group
+
+
+def load_reference(rank, world, cpu_group):
+    """The reference's hook module (imports the reference's helix_a2a from baseline/_ref), or None."""
+    if not os.path.isdir(os.path.join(REF, "helix_a2a")):
+        return None, "baseline/_ref missing"
+    os.environ["HELIX_A2A_BACKEND"] = "native"
+    os.environ["HELIX_A2A_USE_MNNVL"] = "1"
+    sys.path.insert(0, REF)
+    try:
+        spec = importlib.util.spec_from_file_location("ref_dcp_alltoall_helix",
+                                                      os.path.join(REF, "patches", "dcp_alltoall_helix.py"))
+        hook = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(hook)
+        hook.dcp_a2a_ensure_initialized(_Group(rank, world, dist.group.WORLD, cpu_group))
+        return hook, None
+    except Exception as e:  # noqa: BLE001
+        return None, repr(e)[:200]
+    finally:
+        sys.path.remove(REF)
+
+
+def torch_combine(recv_o, recv_lse):
+    """[N,B,Hl,D], [N,B,Hl] -> [B,Hl,D] in the input dtype (fp32 math)."""
+    m = recv_lse.max(dim=0, keepdim=True).values
+    w = torch.exp(recv_lse - m)
+    w = w / w.sum(dim=0, keepdim=True)
+    return (recv_o.float() * w.unsqueeze(-1)).sum(0).to(recv_o.dtype)
+
+
+def make_paths(o, lse, ws, rank, world, hook, group):
+    B, H, D = o.shape
+    Hl = H // world
+    paths = {}
+    paths["helix_fused"] = lambda: helix.alltoall_combine(o, lse, ws, rank, world)
+
+    def helix_exchange():
+        po = o.view(B, world, Hl, D).permute(0, 2, 1, 3).contiguous()
+        st = torch.zeros(B, Hl, world, 2, dtype=torch.float32, device=o.device)
+        st[..., 0] = lse.view(B, world, Hl).permute(0, 2, 1)
+        ro, rs = helix.alltoall(po, st, ws, rank, world)
+        return torch_combine(ro.permute(2, 0, 1, 3), rs[..., 0].permute(2, 0, 1))
+    paths["helix_exchange"] = helix_exchange
+
+    def nccl_torch():
+        so = o.view(B, world, Hl, D).permute(1, 0, 2, 3).contiguous()
+        sl = lse.view(B, world, Hl).permute(1, 0, 2).contiguous()
+        ro, rl = torch.empty_like(so), torch.empty_like(sl)
+        dist.all_to_all_single(ro.view(-1), so.view(-1))
+        dist.all_to_all_single(rl.view(-1), sl.view(-1))
+        return torch_combine(ro, rl)
+    paths["nccl_torch"] = nccl_torch
+
+    def dcp_ag_rs():
+        lses = torch.empty((world,) + lse.shape, dtype=lse.dtype, device=lse.device)
+        dist.all_gather_into_tensor(lses.view(world, -1), lse.view(-1))
+        m = lses.max(dim=0).values
+        denom = torch.exp(lses - m).sum(0)
+        factor = torch.exp(lse - m) / denom                               # this rank's weight per (b, h)
+        corrected = (o.float() * factor.unsqueeze(-1)).to(o.dtype)
+        rs_in = corrected.movedim(0, 1).contiguous()                      # [H, B, D]
+        rs_out = torch.empty(Hl, B, D, dtype=o.dtype, device=o.device)
+        dist.reduce_scatter_tensor(rs_out, rs_in)
+        return rs_out.movedim(0, 1).contiguous()
+    paths["dcp_ag_rs"] = dcp_ag_rs
+
+    if hook is not None:
+        cp = _Group(rank, world, dist.group.WORLD, group)
+        paths["reference"] = lambda: hook.dcp_a2a_lse_reduce(o, lse, cp)
+    return paths
+
+
+def time_path(fn, mode, warmup, iters, world):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    if mode == "graph":
+        per_graph = 10
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                for _ in range(per_graph):
+                    fn()
+        torch.cuda.current_stream().wait_stream(s)
+        reps = max(iters // per_graph, 1)
+        g.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / (reps * per_graph) * 1e3
+    else:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / iters * 1e3
+    t = torch.tensor([us], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.barrier()
+    return float(t.item())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default="mla,gqa")
+    ap.add_argument("--tokens", default="1,8,32,128,256")
+    ap.add_argument("--mode", default="graph", choices=["graph", "eager", "both"])
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--paths", default="")
+    ap.add_argument("--json", default="")
+    ap.add_argument("--no-reference", action="store_true")
+    args = ap.parse_args()
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cpu_group = dist.new_group(backend="gloo")
+    ws = helix.allocate_workspace(world, rank, mnnvl=True, cpu_group=cpu_group)
+    helix.init_workspace(ws, rank, world)
+    dist.barrier()
+    hook, why = (None, "disabled") if args.no_reference else load_reference(rank, world, cpu_group)
+    if rank == 0 and hook is None:
+        print(f"# reference path unavailable: {why}", flush=True)
+
+    shapes = {"mla": (128, 512), "gqa": (64, 128)}            # (total q heads, head dim of the exchanged row)
+    modes = ["graph", "eager"] if args.mode == "both" else [args.mode]
+    rows = []
+    for name in args.shapes.split(","):
+        H, D = shapes[name]
+        if H % world:
+            continue
+        for T in [int(x) for x in args.tokens.split(",")]:
+            torch.manual_seed(123 + T + rank)
+            o = torch.randn(T, H, D, device="cuda").bfloat16()
+            lse = torch.randn(T, H, device="cuda") * 3
+            paths = make_paths(o, lse, ws, rank, world, hook, cpu_group)
+            want = paths["nccl_torch"]().float()
+            errs = {k: (f().float() - want).abs().max().item() for k, f in paths.items()}
+            wire = T * (H // world) * (world - 1) * (D * 2 + 8)            # payload bytes out per rank
+            floor_us = wire / NVLINK_GBS / 1e3
+            for mode in modes:
+                row = {"shape": name, "tokens": T, "H": H, "D": D, "cp": world, "mode": mode,
+                       "payload_bytes_per_rank": wire, "nvlink_floor_us": floor_us, "max_abs_err_vs_nccl_torch": errs}
+                for k, f in paths.items():
+                    if args.paths and k not in args.paths.split(","):
+                        continue
+                    try:
+                        row[k + "_us"] = time_path(f, mode, args.warmup, args.iters, world)
+                    except Exception as e:  # noqa: BLE001
+                        row[k + "_us"] = None
+                        row[k + "_error"] = repr(e)[:120]
+                        torch.cuda.synchronize()
+                if row.get("helix_fused_us"):
+                    row["helix_fused_roofline_frac"] = floor_us / row["helix_fused_us"]
+                    if row.get("nccl_torch_us"):
+                        row["helix_fused_vs_nccl_torch"] = row["helix_fused_us"] / row["nccl_torch_us"]
+                    if row.get("reference_us"):
+                        row["helix_fused_vs_reference"] = row["helix_fused_us"] / row["reference_us"]
+                rows.append(row)
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+            st = helix.check_status(ws, rank, world, raise_on_error=False)
+            if st["code"] != 0:
+                raise SystemExit(f"rank {rank}: exchange status {st}")
+    if rank == 0 and args.json:
+        os.makedirs(os.path.dirname(args.json) or ".", exist_ok=True)
+        with open(args.json, "w") as f:
+            json.dump(rows, f, indent=1)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -304,10 +304,16 @@ static torch::Tensor vmm_as_tensor(uintptr_t handle, int64_t device) {
   int64_t cp = helix::vmm::cp_size(a);
   int64_t elems = (int64_t)helix::vmm::mapped_row_bytes(a) / 8;
   int64_t stride = (int64_t)helix::vmm::row_stride(a) / 8;
-  auto opts = torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, (int)device);
+  // Row 0 may be another GPU's memory, so the pointer's own device is not this rank's device:
+  // name the target device explicitly instead of letting ATen query the pointer.
+  auto opts = torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA);
   // the Python side keeps the allocation alive for as long as the tensor exists
-  return torch::from_blob(reinterpret_cast<void*>(helix::vmm::base_address(a)), {cp, elems}, {stride, 1},
-                          [](void*) {}, opts);
+  return at::for_blob(reinterpret_cast<void*>(helix::vmm::base_address(a)), {cp, elems})
+      .strides({stride, 1})
+      .deleter([](void*) {})
+      .options(opts)
+      .target_device(c10::Device(c10::kCUDA, (c10::DeviceIndex)device))
+      .make_tensor();
 }
 
 PYBIND11_MODULE(_C, m) {

@@ -1,0 +1,156 @@
+"""DCP all-to-all + LSE reduce for vLLM, backed by the fused Helix kernel.
+
+Same hook as the reference's drop-in (``patches/dcp_alltoall_helix.py:391-448``) and as the
+module it replaces in vLLM 0.22 (``vllm/v1/attention/ops/dcp_alltoall.py``)::
+
+    dcp_a2a_lse_reduce(cp_attn_out [B,H,D], cp_attn_lse [B,H], cp_group, ctx=None,
+                       return_lse=False, is_lse_base_on_e=True) -> [B, H/N, D] (, [B, H/N])
+    dcp_a2a_ensure_initialized(cp_group)     # before CUDA-graph capture
+
+Backend switch, read at import like the reference (``patches/dcp_alltoall_helix.py:40,49``):
+``HELIX_A2A_BACKEND=nccl`` (default) keeps the stock path — vLLM's own implementation when vLLM
+is importable, else two ``all_to_all_single`` + a torch combine; ``native`` runs ONE kernel that
+reads ``cp_attn_out`` / ``cp_attn_lse`` in place (no permute / pad / zeros copies), exchanges over
+NVLink and applies the LSE-weighted combine on the receive side.  Base-2 LSEs (FlashInfer) are
+combined natively instead of being converted to base e and back
+(``patches/dcp_alltoall_helix.py:564-567,591-593``).
+
+``apply_runtime_patch()`` swaps the function into the vLLM modules that imported it; the
+``install`` module next to this file rewrites vLLM's file on disk instead.
+"""
+from __future__ import annotations
+
+import logging
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+import helix_a2a_b200 as _helix
+from helix_a2a_b200.ops import reference_math as _rm
+
+logger = logging.getLogger(__name__)
+
+_HELIX_BACKEND = os.environ.get("HELIX_A2A_BACKEND", "nccl").lower()
+_workspace: Optional[torch.Tensor] = None
+_workspace_key = None
+_stock_reduce = None     # vLLM's original function, when it could be imported
+
+
+def _lse_weighted_combine(outputs, lses, return_lse: bool = False, is_lse_base_on_e: bool = True):
+    """Torch reference combine: ``[N,B,H,D]`` + ``[N,B,H]`` -> ``[B,H,D]`` (same rules as the
+    reference's ``_lse_weighted_combine``, ``patches/dcp_alltoall_helix.py:142-207``)."""
+    res = _rm.lse_combine(outputs, lses, return_lse=return_lse, base2=not is_lse_base_on_e)
+    if return_lse:
+        return res[0].to(outputs.dtype), res[1]
+    return res.to(outputs.dtype)
+
+
+def _mnnvl_setting():
+    v = os.environ.get("HELIX_A2A_USE_MNNVL", "auto").strip().lower()
+    if v in ("0", "false", "no", "off"):
+        return False
+    if v in ("1", "true", "yes", "on"):
+        return True
+    return "auto"
+
+
+def _init_workspace(cp_rank: int, cp_size: int, cp_group, device: torch.device):
+    """Collective over the DCP group: allocate, initialise, barrier.  Never inside graph capture."""
+    global _workspace, _workspace_key
+    cpu_group = getattr(cp_group, "cpu_group", None)
+    if device.type == "cpu":
+        ws = _helix.allocate_workspace(cp_size, cp_rank, device="cpu", cpu_group=cpu_group)
+    else:
+        mnnvl = _mnnvl_setting()
+        if mnnvl is False and cp_size > 1:
+            logger.warning("HELIX_A2A_USE_MNNVL=0 gives every process private rows; peers cannot be reached")
+        ws = _helix.allocate_workspace(cp_size, cp_rank, mnnvl=True if mnnvl == "auto" else mnnvl, cpu_group=cpu_group)
+        _helix.init_workspace(ws, cp_rank, cp_size)
+    if cpu_group is not None:
+        dist.barrier(cpu_group)
+    else:
+        dist.barrier(cp_group.device_group)
+    _workspace, _workspace_key = ws, (cp_size, cp_rank, str(device))
+    logger.info("helix workspace ready: rank %d / %d, %s", cp_rank, cp_size, getattr(ws, "_helix_kind", "?"))
+    return ws
+
+
+def _get_workspace(cp_rank: int, cp_size: int, cp_group, device: torch.device):
+    if _workspace is not None and _workspace_key == (cp_size, cp_rank, str(device)):
+        return _workspace
+    if device.type == "cuda" and torch.cuda.is_current_stream_capturing():
+        raise RuntimeError(
+            "the helix workspace is not initialised and cannot be initialised inside CUDA graph capture "
+            "(allocation exchanges handles over the DCP group); call dcp_a2a_ensure_initialized(cp_group) "
+            "before capture, e.g. during model warm-up")
+    return _init_workspace(cp_rank, cp_size, cp_group, device)
+
+
+def dcp_a2a_ensure_initialized(cp_group, device: Optional[torch.device] = None) -> None:
+    """Pre-initialise the workspace for the native backend (no-op otherwise / when already done)."""
+    if _HELIX_BACKEND != "native" or cp_group.world_size == 1:
+        return
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    _get_workspace(cp_group.rank_in_group, cp_group.world_size, cp_group, torch.device(dev))
+
+
+def _nccl_reduce(cp_attn_out, cp_attn_lse, cp_group, return_lse, is_lse_base_on_e):
+    """Stock path: two all_to_all_single + combine (``patches/dcp_alltoall_helix.py:455-504``)."""
+    N = cp_group.world_size
+    B, H, D = cp_attn_out.shape
+    Hl = H // N
+    so = cp_attn_out.contiguous().view(B, N, Hl, D).permute(1, 0, 2, 3).contiguous()
+    sl = cp_attn_lse.contiguous().view(B, N, Hl).permute(1, 0, 2).contiguous()
+    ro, rl = torch.empty_like(so), torch.empty_like(sl)
+    w1 = dist.all_to_all_single(ro.view(-1), so.view(-1), group=cp_group.device_group, async_op=True)
+    w2 = dist.all_to_all_single(rl.view(-1), sl.view(-1), group=cp_group.device_group, async_op=True)
+    w1.wait()
+    w2.wait()
+    return _lse_weighted_combine(ro, rl, return_lse=return_lse, is_lse_base_on_e=is_lse_base_on_e)
+
+
+def dcp_a2a_lse_reduce(cp_attn_out: torch.Tensor, cp_attn_lse: torch.Tensor, cp_group, ctx=None,
+                       return_lse: bool = False, is_lse_base_on_e: bool = True):
+    """Combine partial attention outputs across DCP ranks; returns the head-scattered ``[B, H/N, D]``."""
+    world = cp_group.world_size
+    if world == 1:
+        return (cp_attn_out, cp_attn_lse) if return_lse else cp_attn_out
+    if _HELIX_BACKEND == "native":
+        rank = cp_group.rank_in_group
+        ws = _get_workspace(rank, world, cp_group, cp_attn_out.device)
+        lse = cp_attn_lse if cp_attn_lse.dtype == torch.float32 else cp_attn_lse.float()
+        return _helix.alltoall_combine(cp_attn_out.contiguous(), lse.contiguous(), ws, rank, world,
+                                       return_lse=return_lse, base2=not is_lse_base_on_e)
+    if _stock_reduce is not None:
+        return _stock_reduce(cp_attn_out, cp_attn_lse, cp_group, ctx, return_lse, is_lse_base_on_e)
+    return _nccl_reduce(cp_attn_out, cp_attn_lse, cp_group, return_lse, is_lse_base_on_e)
+
+
+_PATCH_TARGETS = (
+    "vllm.v1.attention.ops.dcp_alltoall",
+    "vllm.v1.attention.backends.flash_attn",
+    "vllm.v1.attention.backends.flashinfer",
+    "vllm.model_executor.layers.attention.mla_attention",
+)
+
+
+def apply_runtime_patch() -> list:
+    """Replace ``dcp_a2a_lse_reduce`` in the vLLM modules that bound it at import; returns their names."""
+    global _stock_reduce
+    import importlib
+    patched = []
+    for name in _PATCH_TARGETS:
+        try:
+            mod = importlib.import_module(name)
+        except Exception:  # noqa: BLE001  (module absent in this vLLM build)
+            continue
+        fn = getattr(mod, "dcp_a2a_lse_reduce", None)
+        if fn is None or fn is dcp_a2a_lse_reduce:
+            continue
+        if _stock_reduce is None and name.endswith("dcp_alltoall"):
+            _stock_reduce = fn
+        setattr(mod, "dcp_a2a_lse_reduce", dcp_a2a_lse_reduce)
+        patched.append(name)
+    return patched
