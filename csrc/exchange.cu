@@ -160,7 +160,8 @@ LaunchInfo plan_launch(const ExchangeParams& p, int channel_override) {
   li.lines_per_message = L;
   li.iters = ceil_div(L, 4);
   li.cooperative = p.ranks_in_launch > 1;
-  li.send_warps = std::max(1, std::min(N - 1, 8));
+  // up to 8 sender warps: with few peers several warps share a peer
+  li.send_warps = N <= 1 ? 1 : (N - 1 <= 8 ? (N - 1) * (8 / (N - 1)) : 8);
   const int max_c = max_channel_count(N, p.sm_count);
 
   int channels = std::min(max_c, std::max(E, 1));

@@ -268,7 +268,10 @@ HELIX_D bool poll_message(const Ctx& cx, const uint8_t* ring, uint64_t q0, int c
 }
 
 // ================================================================================================
-// sender: all messages of channel c to the peers this warp owns
+// sender: messages of channel c to the peers this warp serves.  With few peers several warps share
+// a peer (warp k of K sends messages k, k + K, ...: ring positions are fixed by the message index,
+// so they need no coordination); with many peers one warp walks several.  The words of the next
+// message are loaded before the current one is stored, so the source latency overlaps the stores.
 template <int NIT>
 HELIX_D void sender_warp(const ExchangeParams& p, const Ctx& cx, const RankIO& io, int send_warp, int n_send_warps,
                          int lane) {
@@ -278,8 +281,14 @@ HELIX_D void sender_warp(const ExchangeParams& p, const Ctx& cx, const RankIO& i
   const int payload_words = p.st_words + (p.o_bytes >> 3);
   const int L = ll128::lines_for_words(payload_words);
   const int nchunks = L * kChunksPerLine;
+  const int peers = N - 1;
+  if (peers <= 0) return;
+  const int K = n_send_warps >= peers ? n_send_warps / peers : 1;   // warps per peer
+  const int k = n_send_warps >= peers ? send_warp / peers : 0;
+  if (k >= K) return;
+  const bool single_slab = nchunks <= NIT * 32;
 
-  for (int j = send_warp; j < N - 1; j += n_send_warps) {
+  for (int j = (n_send_warps >= peers ? send_warp % peers : send_warp); j < peers; j += n_send_warps) {
     const int peer = (rank + 1 + j) % N;
     if ((p.skip_peer_mask >> peer) & 1u) continue;
     uint8_t* ring = cx.ws + (int64_t)peer * cx.stride + ring_offset(cx.lay, rank, c);
@@ -287,37 +296,58 @@ HELIX_D void sender_warp(const ExchangeParams& p, const Ctx& cx, const RankIO& i
     const uint64_t head = ld_volatile_8(sinfo + kSinfoHeadOff);
     uint64_t tail = ld_volatile_8(sinfo + kSinfoTailOff);
     bool ok = true;
-    for (int i = 0; i < n_mine && ok; ++i) {
+    uint64_t lo[NIT], hi[NIT];
+    if (single_slab && k < n_mine) load_message<NIT>(p, msg_src(p, io, c + k * C, peer), 0, nchunks, payload_words, lane, lo, hi);
+    for (int i = k; i < n_mine && ok; i += K) {
       const int e = c + i * C;
-      const MsgSrc src = msg_src(p, io, e, peer);
       const uint64_t q0 = head + (uint64_t)i * L;
-      for (int chunk0 = 0; chunk0 < nchunks; chunk0 += NIT * 32) {
-        uint64_t lo[NIT], hi[NIT];
-        // loads are issued before the ring-space check so their latency overlaps it
-        load_message<NIT>(p, src, chunk0, nchunks, payload_words, lane, lo, hi);
-        if (chunk0 == 0) {
-          unsigned spins = 0;
-          while (!ring_has_room(q0 + (uint64_t)L - 1, tail)) {
-            tail = ld_volatile_8(sinfo + kSinfoTailOff);
-            if ((++spins & 31u) == 0u && __any_sync(kFull, give_up(cx))) {
-              if (lane == 0) report(cx, kTimeoutSendSpace, peer, e);
-              ok = false;
-              break;
-            }
-          }
-          if (!ok) break;
+      // ring space for the whole message (bounded wait on the consumed count the receiver stores here)
+      unsigned spins = 0;
+      while (!ring_has_room(q0 + (uint64_t)L - 1, tail)) {
+        tail = ld_volatile_8(sinfo + kSinfoTailOff);
+        if ((++spins & 31u) == 0u && __any_sync(kFull, give_up(cx))) {
+          if (lane == 0) report(cx, kTimeoutSendSpace, peer, e);
+          ok = false;
+          break;
         }
+      }
+      if (!ok) break;
+      if (single_slab) {
+        uint64_t nlo[NIT], nhi[NIT];
+        const bool more = i + K < n_mine;
+        if (more) load_message<NIT>(p, msg_src(p, io, c + (i + K) * C, peer), 0, nchunks, payload_words, lane, nlo, nhi);
 #pragma unroll
         for (int it = 0; it < NIT; ++it) {
-          int ch = chunk0 + it * 32 + lane;
+          int ch = it * 32 + lane;
           if (ch < nchunks) {
             uint64_t h = ((ch & 7) == 7) ? ll128::flag_of(q0 + (uint64_t)(ch >> 3)) : hi[it];
             st_volatile_16(ring + ll128::chunk_ring_offset(q0, ch), lo[it], h);
           }
         }
+        if (more) {
+#pragma unroll
+          for (int it = 0; it < NIT; ++it) {
+            lo[it] = nlo[it];
+            hi[it] = nhi[it];
+          }
+        }
+      } else {
+        const MsgSrc src = msg_src(p, io, e, peer);
+        for (int chunk0 = 0; chunk0 < nchunks; chunk0 += NIT * 32) {
+          load_message<NIT>(p, src, chunk0, nchunks, payload_words, lane, lo, hi);
+#pragma unroll
+          for (int it = 0; it < NIT; ++it) {
+            int ch = chunk0 + it * 32 + lane;
+            if (ch < nchunks) {
+              uint64_t h = ((ch & 7) == 7) ? ll128::flag_of(q0 + (uint64_t)(ch >> 3)) : hi[it];
+              st_volatile_16(ring + ll128::chunk_ring_offset(q0, ch), lo[it], h);
+            }
+          }
+        }
       }
     }
-    if (ok && lane == 0) st_volatile_8(sinfo + kSinfoHeadOff, head + (uint64_t)n_mine * L);
+    // the line count of the call is fixed by its shape, so one warp per peer records it
+    if (ok && k == 0 && lane == 0) st_volatile_8(sinfo + kSinfoHeadOff, head + (uint64_t)n_mine * L);
   }
 }
 
