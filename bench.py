@@ -41,7 +41,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -82,6 +82,7 @@ def parse():
     ap.add_argument("--ctx", type=int, default=CTX)
     ap.add_argument("--batch-per-gpu", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true", help="do not chain the kernels by programmatic dependent launch")
     return ap.parse_args()
 
 
@@ -123,6 +124,8 @@ def barrier(world):
 
 def run_helix(args):
     import torch
+    if not args.no_pdl:
+        os.environ.setdefault("HELIX_A2A_ENABLE_PDL", "1")     # the library's documented knob
     rank, world, group, cpu_group = init_dist(args.gpus)
     from helix_a2a_b200.models.llama_decode import HelixDecodeStack, LlamaDecodeConfig
     from helix_a2a_b200.ops.oproj import check_compute_status
@@ -207,7 +210,7 @@ def run_helix(args):
                        "global_batch": batch, "seq_len": args.ctx, "parallelism": f"cp{world}",
                        "page_size": cfg.page_size, "kv_tokens_per_gpu_per_seq": local_ctx,
                        "l2": "inputs larger than L2 (KV cache read per step: %.1f GB per GPU)" % (kv_bytes / 1e9),
-                       "cuda_graph": not args.no_graph},
+                       "cuda_graph": not args.no_graph, "pdl": os.environ.get("HELIX_A2A_ENABLE_PDL", "0") == "1"},
             "clocks": clocks,
             "e2e": {"value": batch / (ms_e2e * 1e-3), "unit": "tok/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": stack.h2d_bytes_per_step(), "d2h_bytes_per_step": stack.d2h_bytes_per_step()},

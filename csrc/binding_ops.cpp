@@ -197,6 +197,7 @@ torch::Tensor oproj(torch::Tensor x, torch::Tensor w, int64_t splits) {
     p.error_flag = sc.error_flag.data_ptr<int32_t>();
     p.tokens = nt; p.n_pad = n_pad; p.hidden = hidden; p.K = K; p.splits = sp;
     p.stages = helix::oproj_pick_stages(n_pad);
+    p.atoms = helix::oproj_pick_atoms(n_pad);
     p.timeout_ns = env_timeout_ns();
     check_cuda(helix::launch_oproj(p, env_pdl(), stream), "o_proj launch");
   }

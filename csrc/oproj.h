@@ -19,7 +19,7 @@ struct OprojParams {
   float* partial;        // scratch [m_tiles][splits][n_pad][128] fp32 (splits > 1)
   int* counters;         // scratch [m_tiles], zero on entry and on exit
   int* error_flag;
-  int tokens, n_pad, hidden, K, splits, stages;
+  int tokens, n_pad, hidden, K, splits, stages, atoms;   // atoms: 64-wide K atoms per stage (1, 2 or 4)
   unsigned long long timeout_ns;
 };
 
@@ -28,6 +28,7 @@ inline size_t oproj_partial_bytes(int hidden, int splits, int n_pad) {
 }
 int oproj_pick_splits(int hidden, int K, int sm_count);
 int oproj_pick_stages(int n_pad);
+int oproj_pick_atoms(int n_pad);
 int oproj_smem_bytes(int n_pad, int stages);
 
 cudaError_t launch_oproj(const OprojParams& p, bool pdl, cudaStream_t stream);

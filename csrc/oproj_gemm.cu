@@ -6,8 +6,8 @@
 // kernel is bound by streaming W once from HBM:
 //   grid (hidden / 128, splits); each CTA owns one 128-row slab of W and 1/splits of K;
 //   warp 0 (one lane) feeds a ring of shared-memory stages with TMA tiled loads (128-byte swizzle,
-//     W tile [128 x 64] + x tile [n_pad x 64] per stage, no cluster broadcast);
-//   warp 1 (one lane) issues four K=16 UMMAs per stage and releases the stage with
+//     four [128 x 64] W boxes + four [n_pad x 64] x boxes per stage, no cluster broadcast);
+//   warp 1 (one lane) issues sixteen K=16 UMMAs per stage and releases the stage with
 //     tcgen05.commit; after the last stage it commits to the accumulator barrier;
 //   all four warps then read the accumulator with tcgen05.ld (warp w owns TMEM lanes 32w..32w+31)
 //     and write y (bf16) or, with split-K, park an fp32 partial in scratch memory where the last
@@ -28,8 +28,10 @@ namespace {
 using namespace sm100;
 
 constexpr int kBM = 128;   // rows of W per CTA (UMMA M)
-constexpr int kBK = 64;    // K per stage: one 128-byte swizzle atom of bf16
-constexpr int kMaxStages = 12;
+constexpr int kAtomK = 64;  // one 128-byte swizzle atom of bf16
+// A stage holds `atoms` (1, 2 or 4) swizzle atoms along K, so every W row contributes up to 512
+// contiguous bytes per stage and DRAM pages are not opened for 128 bytes at a time.
+constexpr int kMaxStages = 6;
 constexpr int kThreads = 128;
 
 __device__ __forceinline__ void fail(const OprojParams& p, int* s_abort) {
@@ -47,9 +49,12 @@ __global__ void __launch_bounds__(kThreads, 1) oproj_kernel(const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tile = blockIdx.x, split = blockIdx.y;
   const int stages = p.stages;
-  const uint32_t a_bytes = kBM * kBK * 2, b_bytes = (uint32_t)p.n_pad * kBK * 2;
+  const int kAtoms = p.atoms;
+  const int kBK = kAtomK * kAtoms;
+  const uint32_t atom_a_bytes = kBM * kAtomK * 2, atom_b_bytes = (uint32_t)p.n_pad * kAtomK * 2;
+  const uint32_t a_bytes = atom_a_bytes * kAtoms, b_bytes = atom_b_bytes * kAtoms;
   const uint32_t stage_bytes = a_bytes + b_bytes;          // multiples of 1024
-  const int kb_total = p.K / kBK;
+  const int kb_total = (p.K + kBK - 1) / kBK;   // a ragged last block is zero-filled by TMA
   const int kb_per = (kb_total + p.splits - 1) / p.splits;
   const int kb0 = split * kb_per;
   const int nkb = max(0, min(kb_total, kb0 + kb_per) - kb0);
@@ -80,15 +85,24 @@ __global__ void __launch_bounds__(kThreads, 1) oproj_kernel(const __grid_constan
 
   if (warp == 0 && lane == 0) {
     // ---------------- producer ----------------
+    auto load_w = [&](int s, int i) {
+      for (int a = 0; a < kAtoms; ++a)
+        tma_load_2d(smem + (size_t)s * stage_bytes + (size_t)a * atom_a_bytes, &p.w_map, &full_bar[s],
+                    (kb0 + i) * kBK + a * kAtomK, m_tile * kBM);
+    };
+    auto load_x = [&](int s, int i) {
+      for (int a = 0; a < kAtoms; ++a)
+        tma_load_2d(smem + (size_t)s * stage_bytes + a_bytes + (size_t)a * atom_b_bytes, &p.x_map, &full_bar[s],
+                    (kb0 + i) * kBK + a * kAtomK, 0);
+    };
     // weights first: they do not depend on the kernel before us
     const int pre = min(stages, nkb);
     for (int i = 0; i < pre; ++i) {
       mbar_expect_tx(&full_bar[i], stage_bytes);
-      tma_load_2d(smem + (size_t)i * stage_bytes, &p.w_map, &full_bar[i], (kb0 + i) * kBK, m_tile * kBM);
+      load_w(i, i);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (int i = 0; i < pre; ++i)
-      tma_load_2d(smem + (size_t)i * stage_bytes + a_bytes, &p.x_map, &full_bar[i], (kb0 + i) * kBK, 0);
+    for (int i = 0; i < pre; ++i) load_x(i, i);
     for (int i = pre; i < nkb; ++i) {
       const int s = i % stages;
       if (!mbar_wait(&empty_bar[s], (uint32_t)(((i / stages) - 1) & 1), deadline)) {
@@ -96,8 +110,8 @@ __global__ void __launch_bounds__(kThreads, 1) oproj_kernel(const __grid_constan
         break;
       }
       mbar_expect_tx(&full_bar[s], stage_bytes);
-      tma_load_2d(smem + (size_t)s * stage_bytes, &p.w_map, &full_bar[s], (kb0 + i) * kBK, m_tile * kBM);
-      tma_load_2d(smem + (size_t)s * stage_bytes + a_bytes, &p.x_map, &full_bar[s], (kb0 + i) * kBK, 0);
+      load_w(s, i);
+      load_x(s, i);
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer ----------------
@@ -113,10 +127,12 @@ __global__ void __launch_bounds__(kThreads, 1) oproj_kernel(const __grid_constan
       tc_fence_after_sync();
       const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_bytes);
       const uint32_t b_addr = a_addr + a_bytes;
+      for (int a = 0; a < kAtoms; ++a) {
 #pragma unroll
-      for (int k = 0; k < kBK / 16; ++k) {
-        umma_bf16(tmem_d, umma_desc_k_sw128(a_addr + k * 32), umma_desc_k_sw128(b_addr + k * 32), idesc,
-                  (i | k) != 0);
+        for (int k = 0; k < kAtomK / 16; ++k) {
+          umma_bf16(tmem_d, umma_desc_k_sw128(a_addr + a * atom_a_bytes + k * 32),
+                    umma_desc_k_sw128(b_addr + a * atom_b_bytes + k * 32), idesc, (i | a | k) != 0);
+        }
       }
       umma_commit(&empty_bar[s]);          // stage reusable once these MMAs have read it
     }
@@ -205,28 +221,32 @@ __global__ void __launch_bounds__(kThreads, 1) oproj_kernel(const __grid_constan
 
 }  // namespace
 
+int oproj_pick_atoms(int n_pad) { return n_pad <= 64 ? 4 : (n_pad <= 128 ? 2 : 1); }
+
 int oproj_pick_splits(int hidden, int K, int sm_count) {
   // split K only when one CTA per 128-row slab would leave SMs idle for long: each CTA should still
-  // stream at least 16 k-blocks (256 KB of W)
+  // stream at least 256 KB of W
   const int m_tiles = hidden / kBM;
   int splits = std::max(1, sm_count / std::max(m_tiles, 1));
-  const int kb_total = K / kBK;
-  while (splits > 1 && kb_total / splits < 16) --splits;
+  const int kb_total = (K + 255) / 256;
+  while (splits > 1 && kb_total / splits < 4) --splits;
   return std::min(splits, 8);
 }
 
-int oproj_smem_bytes(int n_pad, int stages) { return stages * (kBM * kBK * 2 + n_pad * kBK * 2) + 1024; }
+int oproj_smem_bytes(int n_pad, int stages) {
+  return stages * (kBM + n_pad) * kAtomK * oproj_pick_atoms(n_pad) * 2 + 1024;
+}
 
 int oproj_pick_stages(int n_pad) {
-  const int stage = kBM * kBK * 2 + n_pad * kBK * 2;
-  int s = (200 * 1024) / stage;
+  const int stage = (kBM + n_pad) * kAtomK * oproj_pick_atoms(n_pad) * 2;
+  int s = (222 * 1024) / stage;
   return std::max(2, std::min(s, kMaxStages));
 }
 
 cudaError_t launch_oproj(const OprojParams& p, bool pdl, cudaStream_t stream) {
   if (p.tokens <= 0) return cudaSuccess;
-  if (p.hidden % kBM != 0 || p.K % kBK != 0 || p.n_pad % 16 != 0 || p.n_pad < 16 || p.n_pad > 256 ||
-      p.tokens > p.n_pad || p.stages < 2 || p.stages > kMaxStages || p.splits < 1)
+  if (p.hidden % kBM != 0 || p.K % kAtomK != 0 || p.n_pad % 16 != 0 || p.n_pad < 16 || p.n_pad > 256 ||
+      p.tokens > p.n_pad || (p.atoms != 1 && p.atoms != 2 && p.atoms != 4) || p.stages < 2 || p.stages > kMaxStages || p.splits < 1)
     return cudaErrorInvalidValue;
   const int smem = oproj_smem_bytes(p.n_pad, p.stages);
   cudaError_t e = cudaFuncSetAttribute(oproj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
