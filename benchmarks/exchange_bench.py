@@ -71,7 +71,7 @@ def torch_combine(recv_o, recv_lse):
     return (recv_o.float() * w.unsqueeze(-1)).sum(0).to(recv_o.dtype)
 
 
-def make_paths(o, lse, ws, rank, world, hook, group):
+def make_paths(o, lse, ws, rank, world, hook, group, w_o=None):
     B, H, D = o.shape
     Hl = H // world
     paths = {}
@@ -110,6 +110,15 @@ def make_paths(o, lse, ws, rank, world, hook, group):
     if hook is not None:
         cp = _Group(rank, world, dist.group.WORLD, group)
         paths["reference"] = lambda: hook.dcp_a2a_lse_reduce(o, lse, cp)
+    if w_o is not None:
+        # exchange + combine followed by o_proj (y = x @ w_o^T, this rank's K-slice of the weight)
+        from helix_a2a_b200.ops.oproj import oproj
+        import torch.nn.functional as F
+        paths["oproj:helix_one_kernel"] = lambda: helix.alltoall_combine_oproj(o, lse, w_o, ws, rank, world)
+        paths["oproj:helix_two_kernels"] = lambda: oproj(helix.alltoall_combine(o, lse, ws, rank, world).reshape(B, -1), w_o)
+        paths["oproj:nccl_torch_linear"] = lambda: F.linear(nccl_torch().reshape(B, -1), w_o)
+        if hook is not None:
+            paths["oproj:reference_linear"] = lambda: F.linear(hook.dcp_a2a_lse_reduce(o, lse, cp).reshape(B, -1), w_o)
     return paths
 
 
@@ -163,6 +172,8 @@ def main():
     ap.add_argument("--paths", default="")
     ap.add_argument("--json", default="")
     ap.add_argument("--no-reference", action="store_true")
+    ap.add_argument("--with-oproj", action="store_true", help="also time exchange+combine followed by o_proj")
+    ap.add_argument("--hidden", type=int, default=8192)
     args = ap.parse_args()
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -188,9 +199,14 @@ def main():
             torch.manual_seed(123 + T + rank)
             o = torch.randn(T, H, D, device="cuda").bfloat16()
             lse = torch.randn(T, H, device="cuda") * 3
-            paths = make_paths(o, lse, ws, rank, world, hook, cpu_group)
+            w_o = None
+            if args.with_oproj and T <= 256:
+                w_o = (torch.randn(args.hidden, (H // world) * D, device="cuda") * 0.02).bfloat16()
+            paths = make_paths(o, lse, ws, rank, world, hook, cpu_group, w_o)
             want = paths["nccl_torch"]().float()
-            errs = {k: (f().float() - want).abs().max().item() for k, f in paths.items()}
+            want_y = paths["oproj:nccl_torch_linear"]().float() if w_o is not None else None
+            errs = {k: (f().float() - (want_y if k.startswith("oproj:") else want)).abs().max().item()
+                    for k, f in paths.items()}
             wire = T * (H // world) * (world - 1) * (D * 2 + 8)            # payload bytes out per rank
             floor_us = wire / NVLINK_GBS / 1e3
             for mode in modes:
@@ -205,6 +221,11 @@ def main():
                         row[k + "_us"] = None
                         row[k + "_error"] = repr(e)[:120]
                         torch.cuda.synchronize()
+                if row.get("oproj:helix_one_kernel_us") and w_o is not None:
+                    # roofline of the fused path: slower of NVLink bytes and the HBM stream of this rank's W slice
+                    w_us = w_o.numel() * 2 / 6547.8 / 1e3
+                    row["oproj_floor_us"] = max(floor_us, w_us)
+                    row["oproj_one_kernel_roofline_frac"] = row["oproj_floor_us"] / row["oproj:helix_one_kernel_us"]
                 if row.get("helix_fused_us"):
                     row["helix_fused_roofline_frac"] = floor_us / row["helix_fused_us"]
                     if row.get("nccl_torch_us"):

@@ -10,6 +10,8 @@
 
 #include "attention.h"
 #include "exchange.h"
+#include "fifo.cuh"
+#include "fused.h"
 #include "oproj.h"
 #include "tensor_map.h"
 
@@ -210,6 +212,90 @@ torch::Tensor attn_trace(torch::Tensor like) {
   return sc.trace.clone();
 }
 
+
+// ---- fused exchange + combine + o_proj --------------------------------------------------------------
+// attn_out [B, H, D] bf16, lse [B, H] fp32, w [hidden, (H/cp) * D] bf16 -> y [B, hidden] bf16.
+// emulate: leading [cp] dim on attn_out, lse, w and y; one cooperative launch plays all ranks.
+// Returns (y, x) where x [B, (H/cp) * D] is the combined activation the GEMM consumed.
+std::tuple<torch::Tensor, torch::Tensor> alltoall_combine_oproj(torch::Tensor attn_out, torch::Tensor lse,
+                                                                torch::Tensor w, torch::Tensor workspace,
+                                                                int64_t cp_rank, int64_t cp_size, bool base2,
+                                                                bool emulate, int64_t timeout_ms) {
+  TORCH_CHECK(attn_out.is_cuda() && lse.is_cuda() && w.is_cuda() && workspace.is_cuda(), "inputs must be on CUDA");
+  TORCH_CHECK(attn_out.scalar_type() == at::ScalarType::BFloat16 && w.scalar_type() == at::ScalarType::BFloat16,
+              "attn_out and w must be bfloat16");
+  TORCH_CHECK(lse.scalar_type() == at::ScalarType::Float, "lse must be float32");
+  TORCH_CHECK(attn_out.is_contiguous() && lse.is_contiguous() && w.is_contiguous(), "inputs must be contiguous");
+  const int lead = emulate ? 1 : 0;
+  TORCH_CHECK(attn_out.dim() == 3 + lead && lse.dim() == 2 + lead && w.dim() == 2 + lead, "bad input ranks");
+  const int64_t B = attn_out.size(lead), H = attn_out.size(lead + 1), D = attn_out.size(lead + 2);
+  TORCH_CHECK(H % cp_size == 0, "heads must divide by cp_size");
+  const int64_t Hl = H / cp_size, K = Hl * D, hidden = w.size(lead);
+  TORCH_CHECK(w.size(lead + 1) == K, "w must be [hidden, (H/cp) * D]");
+  TORCH_CHECK(hidden % 128 == 0 && K % 64 == 0 && (D * 2) % 16 == 0, "hidden % 128, K % 64");
+  TORCH_CHECK(B >= 1 && B <= 256, "1..256 tokens per call");
+  TORCH_CHECK(workspace.scalar_type() == at::ScalarType::Long && workspace.dim() == 2 && workspace.size(0) == cp_size,
+              "workspace must be the [cp_size, elems] int64 tensor");
+  const int ranks = emulate ? (int)cp_size : 1;
+  TORCH_CHECK(ranks <= helix::kFusedMaxRanks, "at most ", helix::kFusedMaxRanks, " emulated ranks");
+  if (emulate) TORCH_CHECK(attn_out.size(0) == cp_size && w.size(0) == cp_size, "leading [cp] dim expected");
+  c10::cuda::CUDAGuard guard(attn_out.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  std::vector<int64_t> xs{B, K}, ys{B, hidden};
+  if (emulate) { xs.insert(xs.begin(), cp_size); ys.insert(ys.begin(), cp_size); }
+  torch::Tensor x = torch::empty(xs, attn_out.options());
+  torch::Tensor y = torch::empty(ys, attn_out.options());
+  const int n_pad = (int)((B + 15) / 16 * 16);
+  Scratch& sc = scratch_for(attn_out.device(), hidden / 128 + 1024, 0, 0);
+
+  helix::FusedParams fp{};
+  helix::ExchangeParams& p = fp.ex;
+  for (int r = 0; r < ranks; ++r) {
+    p.io[r].o_src = reinterpret_cast<const uint8_t*>(attn_out.data_ptr()) + (int64_t)r * B * H * D * 2;
+    p.io[r].st_src = reinterpret_cast<const uint8_t*>(lse.data_ptr()) + (int64_t)r * B * H * 4;
+    p.io[r].o_dst = reinterpret_cast<uint8_t*>(x.data_ptr()) + (int64_t)r * B * K * 2;
+    p.io[r].st_dst = nullptr;
+    torch::Tensor xr = emulate ? x[r] : x;
+    torch::Tensor wr = emulate ? w[r] : w;
+    helix::OprojParams& g = fp.gemm[r];
+    g.w_map = mat_map(wr, 128);
+    g.x_map = mat_map(xr, n_pad);
+    g.y = reinterpret_cast<__nv_bfloat16*>(y.data_ptr()) + (int64_t)r * B * hidden;
+    g.y_stride = hidden;
+    g.partial = nullptr;
+    g.counters = sc.counters.data_ptr<int32_t>();
+    g.error_flag = sc.error_flag.data_ptr<int32_t>();
+    g.tokens = (int)B; g.n_pad = n_pad; g.hidden = (int)hidden; g.K = (int)K; g.splits = 1;
+    g.stages = helix::oproj_pick_stages(n_pad);
+    g.atoms = helix::oproj_pick_atoms(n_pad);
+    g.timeout_ns = timeout_ms > 0 ? (unsigned long long)timeout_ms * 1000000ull : env_timeout_ns();
+  }
+  p.workspace = reinterpret_cast<uint64_t*>(workspace.data_ptr());
+  p.row_stride_bytes = workspace.stride(0) * 8;
+  p.sm_count = helix::device_sm_count();
+  p.cp_size = (int)cp_size;
+  p.rank_base = emulate ? 0 : (int)cp_rank;
+  p.ranks_in_launch = ranks;
+  p.outer = (int)B; p.inner = (int)Hl;
+  p.o_sb = H * D * 2; p.o_sp = Hl * D * 2; p.o_sh = D * 2;
+  p.st_sb = H * 4; p.st_sp = Hl * 4; p.st_sh = 4;
+  p.lse_scalar = 1;
+  p.od_se = D * 2;
+  p.o_bytes = (int)(D * 2);
+  p.st_words = 1;
+  p.is_bf16 = 1;
+  p.mode = helix::kModeCombine;
+  p.stats_mode = 0;
+  p.base2 = base2 ? 1 : 0;
+  p.timeout_ns = timeout_ms > 0 ? (unsigned long long)timeout_ms * 1000000ull : env_timeout_ns();
+  const char* ch = std::getenv("HELIX_A2A_CHANNEL_COUNT");
+  cudaError_t e = helix::launch_exchange_oproj(fp, ch ? std::max(std::atoi(ch), 0) : 0, env_pdl(), stream, nullptr);
+  TORCH_CHECK(e != cudaErrorNotSupported, "helix: fused exchange+o_proj does not fit this shape on the device; "
+              "run alltoall_combine and oproj separately");
+  check_cuda(e, "fused exchange+o_proj launch");
+  return std::make_tuple(y, x);
+}
+
 int64_t read_error_flag(torch::Tensor like) {
   Scratch& sc = scratch_for(like.device(), 1, 0, 0);
   return sc.error_flag.item<int>();
@@ -229,6 +315,10 @@ void register_compute_ops(torch::Library& m) {
       "lse_base2, bool hnd, int splits, int max_seq_len) -> (Tensor, Tensor)",
       &gqa_decode);
   m.def("oproj(Tensor x, Tensor w, int splits) -> Tensor", &oproj);
+  m.def(
+      "alltoall_combine_oproj(Tensor attn_out, Tensor lse, Tensor w, Tensor workspace, int cp_rank, int cp_size, bool "
+      "base2, bool emulate, int timeout_ms) -> (Tensor, Tensor)",
+      &alltoall_combine_oproj);
   m.def("read_error_flag(Tensor like) -> int", &read_error_flag);
   m.def("attn_trace(Tensor like) -> Tensor", &attn_trace);
   m.def("clear_error_flag(Tensor like) -> ()", &clear_error_flag);

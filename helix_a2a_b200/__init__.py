@@ -15,6 +15,7 @@ from .api import (
     HelixTimeoutError,
     alltoall,
     alltoall_combine,
+    alltoall_combine_oproj,
     allocate_workspace,
     check_status,
     debug_info,
@@ -30,6 +31,7 @@ __all__ = [
     "init_workspace",
     "alltoall",
     "alltoall_combine",
+    "alltoall_combine_oproj",
     "check_status",
     "reset_workspace",
     "debug_info",

@@ -160,6 +160,31 @@ def alltoall_combine(attn_out: torch.Tensor, lse: torch.Tensor, workspace: torch
     return (out, glse) if return_lse else out
 
 
+def alltoall_combine_oproj(attn_out: torch.Tensor, lse: torch.Tensor, w_o: torch.Tensor, workspace: torch.Tensor,
+                           cp_rank: int, cp_size: int, *, base2: bool = False, timeout_ms: int = 0) -> torch.Tensor:
+    """Exchange + LSE combine + o_proj in one kernel launch.
+
+    ``attn_out [B, H, D]`` (bf16), ``lse [B, H]`` (fp32), ``w_o [hidden, (H/N) * D]`` (this rank's
+    K-slice of the o_proj weight, bf16) -> ``y [B, hidden]`` (this rank's partial sum).  The weight
+    slabs start streaming before the exchange has finished.  On CPU tensors, or when the shape does
+    not fit one co-resident grid, the two steps run one after the other.
+    """
+    from .ops import oproj as _oproj
+    B = attn_out.shape[0]
+    if isinstance(workspace, CpuWorkspace) or not attn_out.is_cuda or cp_size == 1:
+        x = alltoall_combine(attn_out, lse, workspace, cp_rank, cp_size, base2=base2) if cp_size > 1 else attn_out
+        return _oproj.oproj(x.reshape(B, -1), w_o)
+    from .ops._ext import ops
+    try:
+        y, _ = ops().alltoall_combine_oproj(attn_out, lse, w_o, workspace, cp_rank, cp_size, base2, False, timeout_ms)
+        return y
+    except RuntimeError as e:
+        if "does not fit" not in str(e):
+            raise
+        x = alltoall_combine(attn_out, lse, workspace, cp_rank, cp_size, base2=base2)
+        return _oproj.oproj(x.reshape(B, -1), w_o)
+
+
 def check_status(workspace: torch.Tensor, cp_rank: int, cp_size: int, *, raise_on_error: bool = True) -> dict:
     """Read the status block of the local row (synchronises the current stream)."""
     if isinstance(workspace, CpuWorkspace):

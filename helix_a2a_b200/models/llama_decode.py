@@ -50,10 +50,11 @@ class HelixDecodeStack:
 
     def __init__(self, cfg: LlamaDecodeConfig, *, batch: int, local_ctx: int, cp_size: int = 1, cp_rank: int = 0,
                  group: Optional[dist.ProcessGroup] = None, device="cuda", seed: int = 0,
-                 workspace: Optional[torch.Tensor] = None, kv_std: float = 1.0):
+                 workspace: Optional[torch.Tensor] = None, kv_std: float = 1.0, fuse_oproj: bool = True):
         assert cfg.n_q_heads % cp_size == 0, "query heads must divide evenly over the CP ranks"
         self.cfg, self.batch, self.local_ctx = cfg, batch, local_ctx
         self.cp_size, self.cp_rank, self.group = cp_size, cp_rank, group
+        self.fuse_oproj = fuse_oproj
         self.device = torch.device(device)
         self.heads_local = cfg.n_q_heads // cp_size
         self.k_local = self.heads_local * cfg.head_dim
@@ -95,6 +96,9 @@ class HelixDecodeStack:
         cfg = self.cfg
         o, lse = attention.gqa_decode(q, self.k_cache[l], self.v_cache[l], self.block_table, self.seq_lens,
                                       scale=self.scale, max_seq_len=self.local_ctx)
+        if self.cp_size > 1 and self.fuse_oproj:
+            # exchange + combine + o_proj in one launch: W_o streams while the exchange is in flight
+            return api.alltoall_combine_oproj(o, lse, self.w_o[l], self.workspace, self.cp_rank, self.cp_size)
         if self.cp_size > 1:
             x = api.alltoall_combine(o, lse, self.workspace, self.cp_rank, self.cp_size)
         else:
@@ -153,7 +157,7 @@ class HelixDecodeStack:
 
     # ---- accounting ------------------------------------------------------------------------------
     def kernels_per_step(self) -> int:
-        return self.cfg.n_layers * (3 if self.cp_size > 1 else 2)
+        return self.cfg.n_layers * ((2 if self.fuse_oproj else 3) if self.cp_size > 1 else 2)
 
     def h2d_bytes_per_step(self) -> int:
         c = self.cfg

@@ -84,6 +84,24 @@ def main():
         check(f"fused combine B={B} H={H} D={D} base2={base2}",
               (got.float() - want[rank]).abs().max().item() < 2e-2 and (glse - wlse[rank]).abs().max().item() < 1e-4)
 
+    # one-kernel exchange + combine + o_proj against the oracle
+    for (B, H, D, hidden) in ((8, 64, 128, 1024), (1, 64, 128, 8192), (33, 64, 128, 512)):
+        if H % world:
+            continue
+        g = torch.Generator(device="cuda").manual_seed(2000 + B)
+        outs = torch.randn(world, B, H, D, device="cuda", generator=g).bfloat16()
+        lses = torch.randn(world, B, H, device="cuda", generator=g) * 2
+        w_all = (torch.randn(world, hidden, (H // world) * D, device="cuda", generator=g) * 0.05).bfloat16()
+        ok = True
+        for _ in range(3):
+            y = helix.alltoall_combine_oproj(outs[rank].contiguous(), lses[rank].contiguous(), w_all[rank].contiguous(),
+                                             ws, rank, world)
+            torch.cuda.synchronize()
+            xr = rm.head_scatter_combine_reference(outs, lses)[rank].reshape(B, -1)
+            ref = rm.oproj_reference(xr.bfloat16(), w_all[rank])
+            ok &= (y.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+        check(f"one-kernel exchange+combine+o_proj B={B} hidden={hidden}", ok)
+
     # many calls back to back without re-init (rings wrap), ranks deliberately skewed
     g = torch.Generator(device="cuda").manual_seed(5)
     outs = torch.randn(world, 16, 64, 128, device="cuda", generator=g).bfloat16()

@@ -238,3 +238,26 @@ def test_public_api_cp1(helix):
     assert out.shape == (3, 8, 128)
     info = helix.debug_info(ws)
     assert info["workspace_kind"] == "device"
+
+
+@pytest.mark.parametrize("cp,B,H,D,hidden", [(2, 8, 16, 128, 512), (4, 3, 32, 128, 1024), (2, 64, 16, 128, 256),
+                                              (4, 1, 32, 512, 512)])
+def test_fused_exchange_combine_oproj(helix, cp, B, H, D, hidden):
+    """One launch: exchange + combine + tcgen05 o_proj, all ranks played on one GPU."""
+    from helix_a2a_b200.ops import reference_math as rm
+    torch.manual_seed(B + hidden)
+    ws = _ws(helix, cp)
+    K = (H // cp) * D
+    outs = torch.randn(cp, B, H, D, device="cuda").bfloat16()
+    lses = torch.randn(cp, B, H, device="cuda") * 2
+    w = (torch.randn(cp, hidden, K, device="cuda") * 0.05).bfloat16()
+    for it in range(3):                               # counters re-arm themselves between launches
+        y, x = _ops().alltoall_combine_oproj(outs, lses, w, ws, 0, cp, False, True, 0)
+        torch.cuda.synchronize()
+        want_x = rm.head_scatter_combine_reference(outs, lses)                     # [cp, B, Hl, D]
+        assert (x.float().view(cp, B, H // cp, D) - want_x).abs().max() < 2e-2
+        for r in range(cp):
+            ref = rm.oproj_reference(x[r], w[r])
+            assert (y[r].float() - ref).abs().max() < 3e-2 * max(1.0, ref.abs().max().item()), (it, r)
+    for r in range(cp):
+        assert helix.check_status(ws, r, cp)["code"] == 0
