@@ -45,4 +45,32 @@ int gqa_pick_ctas(int B, int Hkv, int max_seq_len, int sm_count);
 
 cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t stream);
 
+// ---- MLA (latent) decode attention over a block-scaled fp8 cache ------------------------------------
+// Absorbed form: scores = (q_nope . ckv + q_pe . kpe) * scale, values = ckv (the 512-d latent).
+struct MlaDecodeParams {
+  const __nv_bfloat16* q_nope;   // [B, 128, 512] contiguous (already multiplied by W_uk)
+  const __nv_bfloat16* q_pe;     // [B, 128, 64] contiguous
+  const uint8_t* ckv;            // [pages * page_size, 512] fp8 e4m3
+  const float* scales;           // [pages * page_size, 4]  one scale per 128 latent values
+  const __nv_bfloat16* kpe;      // [pages * page_size, 64] rope keys
+  const int32_t* block_table;    // [B, bt_stride]
+  int64_t bt_stride;
+  const int32_t* seq_lens;       // [B]
+  __nv_bfloat16* o;              // [B, 128, 512] normalised partial output (latent space)
+  float* lse;                    // [B, 128]
+  float* part_o;                 // scratch [ctas, 2, 128, 512] fp32
+  float* part_lse;               // scratch [ctas, 2, 128]
+  int* counters;                 // scratch [B], zero on entry and on exit
+  int* error_flag;
+  int B, page_size, ctas;
+  float scale;
+  int lse_base2;
+  unsigned long long timeout_ns;
+};
+constexpr int kMlaMaxCtas = 296;
+inline size_t mla_part_o_floats(int ctas) { return (size_t)ctas * 2 * 128 * 512; }
+inline size_t mla_part_lse_floats(int ctas) { return (size_t)ctas * 2 * 128; }
+int mla_pick_ctas(int B, int max_seq_len, int sm_count);
+cudaError_t launch_mla_decode(const MlaDecodeParams& p, bool pdl, cudaStream_t stream);
+
 }  // namespace helix

@@ -166,6 +166,64 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   return std::make_tuple(o, lse);
 }
 
+
+// ---- MLA fp8 paged decode attention -----------------------------------------------------------------
+std::tuple<torch::Tensor, torch::Tensor> mla_decode(torch::Tensor q_nope, torch::Tensor q_pe, torch::Tensor ckv,
+                                                    torch::Tensor scales, torch::Tensor kpe, torch::Tensor block_table,
+                                                    torch::Tensor seq_lens, double scale, bool lse_base2, int64_t ctas,
+                                                    int64_t max_seq_len) {
+  TORCH_CHECK(q_nope.is_cuda() && q_pe.is_cuda() && ckv.is_cuda() && scales.is_cuda() && kpe.is_cuda() &&
+                  block_table.is_cuda() && seq_lens.is_cuda(), "all inputs must be on CUDA");
+  TORCH_CHECK(q_nope.scalar_type() == at::ScalarType::BFloat16 && q_pe.scalar_type() == at::ScalarType::BFloat16 &&
+                  kpe.scalar_type() == at::ScalarType::BFloat16, "q_nope / q_pe / kpe must be bfloat16");
+  TORCH_CHECK(ckv.element_size() == 1, "ckv must be fp8 e4m3 (1 byte per element)");
+  TORCH_CHECK(scales.scalar_type() == at::ScalarType::Float, "scales must be float32");
+  TORCH_CHECK(q_nope.dim() == 3 && q_nope.size(1) == 128 && q_nope.size(2) == 512 && q_nope.is_contiguous(),
+              "q_nope must be contiguous [B, 128, 512]");
+  TORCH_CHECK(q_pe.dim() == 3 && q_pe.size(0) == q_nope.size(0) && q_pe.size(1) == 128 && q_pe.size(2) == 64 &&
+                  q_pe.is_contiguous(), "q_pe must be contiguous [B, 128, 64]");
+  TORCH_CHECK(ckv.dim() == 3 && ckv.size(2) == 512 && ckv.is_contiguous(), "ckv must be contiguous [pages, page, 512]");
+  TORCH_CHECK(scales.dim() == 3 && scales.size(0) == ckv.size(0) && scales.size(1) == ckv.size(1) && scales.size(2) == 4 &&
+                  scales.is_contiguous(), "scales must be contiguous [pages, page, 4]");
+  TORCH_CHECK(kpe.dim() == 3 && kpe.size(0) == ckv.size(0) && kpe.size(1) == ckv.size(1) && kpe.size(2) == 64 &&
+                  kpe.is_contiguous(), "kpe must be contiguous [pages, page, 64]");
+  TORCH_CHECK(block_table.scalar_type() == at::ScalarType::Int && seq_lens.scalar_type() == at::ScalarType::Int &&
+                  block_table.dim() == 2 && block_table.stride(1) == 1 && seq_lens.is_contiguous(),
+              "block_table [B, n] / seq_lens [B] must be int32");
+  const int B = (int)q_nope.size(0), page = (int)ckv.size(1);
+  TORCH_CHECK(page % 16 == 0, "page size must be a multiple of 16");
+  c10::cuda::CUDAGuard guard(q_nope.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  torch::Tensor o = torch::empty({B, 128, 512}, q_nope.options());
+  torch::Tensor lse = torch::empty({B, 128}, q_nope.options().dtype(torch::kFloat32));
+  if (B == 0) return std::make_tuple(o, lse);
+  int nc = ctas > 0 ? (int)std::min<int64_t>(ctas, helix::kMlaMaxCtas)
+                    : helix::mla_pick_ctas(B, (int)std::max<int64_t>(max_seq_len, 1), helix::device_sm_count());
+  Scratch& sc = scratch_for(q_nope.device(), (int64_t)B + 1024, (int64_t)helix::mla_part_o_floats(nc),
+                            (int64_t)helix::mla_part_lse_floats(nc));
+  helix::MlaDecodeParams p{};
+  p.q_nope = reinterpret_cast<const __nv_bfloat16*>(q_nope.data_ptr());
+  p.q_pe = reinterpret_cast<const __nv_bfloat16*>(q_pe.data_ptr());
+  p.ckv = reinterpret_cast<const uint8_t*>(ckv.data_ptr());
+  p.scales = scales.data_ptr<float>();
+  p.kpe = reinterpret_cast<const __nv_bfloat16*>(kpe.data_ptr());
+  p.block_table = block_table.data_ptr<int32_t>();
+  p.bt_stride = block_table.stride(0);
+  p.seq_lens = seq_lens.data_ptr<int32_t>();
+  p.o = reinterpret_cast<__nv_bfloat16*>(o.data_ptr());
+  p.lse = lse.data_ptr<float>();
+  p.part_o = sc.part_a.data_ptr<float>();
+  p.part_lse = sc.part_b.data_ptr<float>();
+  p.counters = sc.counters.data_ptr<int32_t>();
+  p.error_flag = sc.error_flag.data_ptr<int32_t>();
+  p.B = B; p.page_size = page; p.ctas = nc;
+  p.scale = (float)scale;
+  p.lse_base2 = lse_base2 ? 1 : 0;
+  p.timeout_ns = env_timeout_ns();
+  check_cuda(helix::launch_mla_decode(p, env_pdl(), stream), "mla decode launch");
+  return std::make_tuple(o, lse);
+}
+
 // ---- o_proj ----------------------------------------------------------------------------------------
 torch::Tensor oproj(torch::Tensor x, torch::Tensor w, int64_t splits) {
   TORCH_CHECK(x.is_cuda() && w.is_cuda(), "inputs must be on CUDA");
@@ -314,6 +372,10 @@ void register_compute_ops(torch::Library& m) {
       "gqa_decode(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_table, Tensor seq_lens, float scale, bool "
       "lse_base2, bool hnd, int splits, int max_seq_len) -> (Tensor, Tensor)",
       &gqa_decode);
+  m.def(
+      "mla_decode(Tensor q_nope, Tensor q_pe, Tensor ckv, Tensor scales, Tensor kpe, Tensor block_table, Tensor seq_lens, "
+      "float scale, bool lse_base2, int ctas, int max_seq_len) -> (Tensor, Tensor)",
+      &mla_decode);
   m.def("oproj(Tensor x, Tensor w, int splits) -> Tensor", &oproj);
   m.def(
       "alltoall_combine_oproj(Tensor attn_out, Tensor lse, Tensor w, Tensor workspace, int cp_rank, int cp_size, bool "

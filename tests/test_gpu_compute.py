@@ -81,3 +81,43 @@ def test_oproj_on_column_slice_of_full_weight(built):
     y = oproj(x, w_slice)
     ref = x.float() @ w_slice.float().t()
     assert (y.float() - ref).abs().max() < 2e-2
+
+
+def _mla_case(seq_lens, page=16, seed=0):
+    from helix_a2a_b200.ops import reference_math as rm
+    torch.manual_seed(seed)
+    B = len(seq_lens)
+    max_blocks = max((s + page - 1) // page for s in seq_lens) + 1
+    n_pages = B * max_blocks + 2
+    bt = torch.randperm(n_pages)[:B * max_blocks].view(B, max_blocks).int().cuda()
+    lat = torch.randn(n_pages, page, 512, device="cuda")
+    ckv, scales = rm.quantize_fp8_blockscaled(lat, 128)
+    kpe = torch.randn(n_pages, page, 64, device="cuda").bfloat16()
+    qn = (torch.randn(B, 128, 512, device="cuda") * 0.5).bfloat16()
+    qp = (torch.randn(B, 128, 64, device="cuda") * 0.5).bfloat16()
+    return qn, qp, ckv, scales, kpe, bt, torch.tensor(seq_lens, dtype=torch.int32, device="cuda")
+
+
+@pytest.mark.parametrize("seq_lens,ctas", [([32], 1), ([100, 7, 64], 1), ([1000, 333], 3), ([4096, 2000, 17, 0], 0),
+                                           ([700] * 5, 7)])
+def test_mla_fp8_decode_matches_fp32_reference(built, seq_lens, ctas):
+    import math
+    from helix_a2a_b200.ops import attention, reference_math as rm
+    from helix_a2a_b200.ops.oproj import check_compute_status
+    qn, qp, ckv, scales, kpe, bt, sl = _mla_case(seq_lens, seed=len(seq_lens))
+    scale = 1.0 / math.sqrt(128 + 64)
+    o, lse = attention.mla_decode(qn, qp, ckv, scales, kpe, bt, sl, scale=scale, ctas=ctas, max_seq_len=max(seq_lens))
+    torch.cuda.synchronize()
+    check_compute_status(qn)
+    lat = rm.dequantize_fp8_blockscaled(ckv, scales, 128)
+    for b, n in enumerate(seq_lens):
+        if n == 0:
+            assert (o[b] == 0).all() and (lse[b] == float("-inf")).all()
+            continue
+        npg = (n + 15) // 16
+        idx = bt[b, :npg].long()
+        c = lat[idx].reshape(-1, 512)[:n]
+        k = kpe[idx].reshape(-1, 64)[:n].float()
+        o_ref, l_ref = rm.mla_partial_attention(qn[b:b + 1].float(), qp[b:b + 1].float(), c, k, scale)
+        assert (o[b].float() - o_ref[0]).abs().max() < 3e-2, (b, n)
+        assert (lse[b] - l_ref[0]).abs().max() < 5e-3, (b, n)
