@@ -35,3 +35,24 @@ def test_decode_stack_matches_oracle_and_graph_pdl_replay(native_built):
     finally:
         del os.environ["HELIX_A2A_ENABLE_PDL"]
     check_compute_status(q)
+
+
+def test_mla_decode_stack_matches_oracle(native_built):
+    from helix_a2a_b200.models.deepseek_mla_decode import MlaDecodeConfig, MlaDecodeStack
+    from helix_a2a_b200.ops import reference_math as rm
+    cfg = MlaDecodeConfig.tiny()
+    stack = MlaDecodeStack(cfg, batch=2, local_ctx=300, device="cuda")
+    qn = (torch.randn(cfg.n_layers, 2, 128, 512, device="cuda") * 0.3).bfloat16()
+    qp = (torch.randn(cfg.n_layers, 2, 128, 64, device="cuda") * 0.3).bfloat16()
+    y = stack.decode_step(qn, qp)
+    l = cfg.n_layers - 1
+    lat = rm.dequantize_fp8_blockscaled(stack.ckv[l], stack.scales[l], 128)
+    outs = []
+    for b in range(2):
+        idx = stack.block_table[b].long()
+        c = lat[idx].reshape(-1, 512)[:300]
+        k = stack.kpe[l][idx].reshape(-1, 64)[:300].float()
+        o, _ = rm.mla_partial_attention(qn[l, b:b + 1].float(), qp[l, b:b + 1].float(), c, k, stack.scale)
+        outs.append(o)
+    ref = rm.oproj_reference(torch.cat(outs).reshape(2, -1).bfloat16(), stack.w_o[l])
+    assert (y.float() - ref).abs().max() < 5e-2 * max(1.0, ref.abs().max().item())
