@@ -4,6 +4,7 @@
     python benchmarks/profile_case.py attn      # GQA decode, B=8, 16K tokens per sequence (537 MB of KV)
     python benchmarks/profile_case.py oproj     # o_proj, 8 tokens, K=8192, hidden 8192 (134 MB of W)
     python benchmarks/profile_case.py exchange  # fused exchange+combine, 4 ranks played by one launch
+    python benchmarks/profile_case.py mla       # MLA fp8 decode, B=8, 16K tokens per sequence
 """
 import os
 import sys
@@ -33,6 +34,19 @@ def main():
         x = torch.randn(8, 8192, device="cuda").bfloat16()
         for _ in range(launches):
             oproj(x, w)
+    elif which == "mla":
+        import math
+        from helix_a2a_b200.ops import attention, reference_math as rm
+        B, ctx, page = 8, 16384, 16
+        pages = B * ctx // page
+        bt = torch.randperm(pages).int().view(B, -1).cuda()
+        sl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        ckv, sc = rm.quantize_fp8_blockscaled(torch.randn(pages, page, 512, device="cuda"), 128)
+        kpe = torch.randn(pages, page, 64, device="cuda").bfloat16()
+        qn = (torch.randn(B, 128, 512, device="cuda") * 0.3).bfloat16()
+        qp = (torch.randn(B, 128, 64, device="cuda") * 0.3).bfloat16()
+        for _ in range(launches):
+            attention.mla_decode(qn, qp, ckv, sc, kpe, bt, sl, scale=1 / math.sqrt(192), max_seq_len=ctx)
     else:
         import helix_a2a_b200 as helix
         from helix_a2a_b200.ops._ext import ops
