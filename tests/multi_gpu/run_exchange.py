@@ -134,8 +134,58 @@ def main():
     torch.cuda.synchronize()
     check("CUDA graph replay", (got_g.float() - want).abs().max().item() < 2e-2)
 
+    # 10^4 back-to-back calls without re-initialisation (graph of 100 calls replayed 100 times)
+    st2 = torch.cuda.Stream()
+    st2.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st2):
+        g100 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g100, stream=st2):
+            for _ in range(100):
+                got_many = helix.alltoall_combine(o_in, l_in, ws, rank, world)
+    torch.cuda.current_stream().wait_stream(st2)
+    dist.barrier()
+    for _ in range(100):
+        g100.replay()
+    torch.cuda.synchronize()
+    check("10000 calls without re-init", (got_many.float() - want).abs().max().item() < 2e-2)
+
+    # the vLLM hook with the native backend (same call the attention backends make)
+    os.environ["HELIX_A2A_BACKEND"] = "native"
+    import importlib
+    import helix_a2a_b200.vllm_patch.dcp_alltoall_helix as hook
+    hook = importlib.reload(hook)
+
+    from types import SimpleNamespace
+    _G = SimpleNamespace(rank_in_group=rank, world_size=world, device_group=dist.group.WORLD, cpu_group=cpu_group)
+    hook.dcp_a2a_ensure_initialized(_G)
+    hv, hl = hook.dcp_a2a_lse_reduce(o_in, l_in, _G, return_lse=True)
+    wv, wl = rm.head_scatter_combine_reference(outs, lses, return_lse=True)
+    check("vLLM hook, native backend", (hv.float() - wv[rank]).abs().max().item() < 2e-2
+          and (hl - wl[rank]).abs().max().item() < 1e-4)
+    hb = hook.dcp_a2a_lse_reduce(o_in, l_in * 1.4426950408889634, _G, is_lse_base_on_e=False)
+    check("vLLM hook, base-2 LSE", (hb.float() - wv[rank]).abs().max().item() < 2e-2)
+
     st_ = helix.check_status(ws, rank, world, raise_on_error=False)
     check("status clean", st_["code"] == 0)
+
+    # a sender that silently skips one peer: that peer's bounded wait runs out, it reports a status
+    # and returns; after reset_workspace (barrier, re-init, barrier) the same workspace works again
+    dist.barrier()
+    victim = 1 % world
+    skip = (1 << victim) if rank == 0 else 0
+    po = torch.randn(4, world, 128, device="cuda").bfloat16()
+    ps = torch.randn(4, world, 2, device="cuda")
+    torch.ops.helix_a2a_b200.alltoall_debug(po, ps, ws, rank, world, False, skip, 100)
+    torch.cuda.synchronize()
+    stv = helix.check_status(ws, rank, world, raise_on_error=False)
+    check("timeout reported on the skipped peer only",
+          (stv["code"] == 1 and stv["peer"] == 0) if rank == victim else stv["code"] == 0)
+    helix.reset_workspace(ws, rank, world, group=cpu_group)
+    ro2, rs2 = helix.alltoall(po, ps, ws, rank, world)
+    want_o2, want_s2 = nccl_alltoall(po, ps)
+    torch.cuda.synchronize()
+    check("exchange works again after reset_workspace", torch.equal(ro2, want_o2) and torch.equal(rs2, want_s2)
+          and helix.check_status(ws, rank, world, raise_on_error=False)["code"] == 0)
     dist.barrier()
     dist.destroy_process_group()
     if fails:
