@@ -311,7 +311,13 @@ std::tuple<torch::Tensor, torch::Tensor> alltoall_combine_oproj(torch::Tensor at
   torch::Tensor x = torch::empty(xs, attn_out.options());
   torch::Tensor y = torch::empty(ys, attn_out.options());
   const int n_pad = (int)((B + 15) / 16 * 16);
-  Scratch& sc = scratch_for(attn_out.device(), hidden / 128 + 1024, 0, 0);
+  // split K like the stand-alone GEMM does, as long as the slabs still leave SMs for the exchange
+  int gsplits = emulate ? 1 : helix::oproj_pick_splits((int)hidden, (int)K, helix::device_sm_count());
+  // ... and the exchange keeps at least half a channel per entry (up to 32 channels)
+  const int64_t want_channels = std::max<int64_t>(std::min<int64_t>(B * Hl, 64) / 2, 1);
+  while (gsplits > 1 && (hidden / 128) * gsplits > helix::device_sm_count() - want_channels) --gsplits;
+  Scratch& sc = scratch_for(attn_out.device(), hidden / 128 + 1024,
+                            gsplits > 1 ? (int64_t)helix::oproj_partial_bytes((int)hidden, gsplits, n_pad) / 4 : 0, 0);
 
   helix::FusedParams fp{};
   helix::ExchangeParams& p = fp.ex;
@@ -327,10 +333,10 @@ std::tuple<torch::Tensor, torch::Tensor> alltoall_combine_oproj(torch::Tensor at
     g.x_map = mat_map(xr, n_pad);
     g.y = reinterpret_cast<__nv_bfloat16*>(y.data_ptr()) + (int64_t)r * B * hidden;
     g.y_stride = hidden;
-    g.partial = nullptr;
-    g.counters = sc.counters.data_ptr<int32_t>();
+    g.partial = gsplits > 1 ? sc.part_a.data_ptr<float>() : nullptr;
+    g.counters = sc.counters.data_ptr<int32_t>() + (sc.counters.numel() - hidden / 128);
     g.error_flag = sc.error_flag.data_ptr<int32_t>();
-    g.tokens = (int)B; g.n_pad = n_pad; g.hidden = (int)hidden; g.K = (int)K; g.splits = 1;
+    g.tokens = (int)B; g.n_pad = n_pad; g.hidden = (int)hidden; g.K = (int)K; g.splits = gsplits;
     g.stages = helix::oproj_pick_stages(n_pad);
     g.atoms = helix::oproj_pick_atoms(n_pad);
     g.timeout_ns = timeout_ms > 0 ? (unsigned long long)timeout_ms * 1000000ull : env_timeout_ns();

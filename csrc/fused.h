@@ -10,9 +10,9 @@ constexpr int kFusedMaxRanks = 4;   // ranks one launch can play in single-proce
 
 struct FusedParams {
   ExchangeParams ex;                 // combine mode, native layout; o_dst is the x buffer of the GEMM
-  OprojParams gemm[kFusedMaxRanks];  // per emulated rank (index 0 in multi-process use); splits must be 1
+  OprojParams gemm[kFusedMaxRanks];  // per emulated rank (index 0 in multi-process use); split-K only without emulation
   int exchange_ctas;                 // CTAs [0, exchange_ctas) exchange, the rest run the GEMM
-  int gemm_ctas;                     // hidden / 128
+  int gemm_ctas;                     // hidden / 128 * splits
 };
 
 // Launches the fused kernel; returns cudaErrorNotSupported when the GEMM slabs plus at least one

@@ -81,8 +81,9 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   const OprojParams& gp = fp.gemm[blockIdx.y];
   const unsigned int rows = (unsigned int)(p.outer * p.inner);
   const unsigned int n_gemm = (unsigned int)fp.gemm_ctas;
+  const int gidx = (int)blockIdx.x - fp.exchange_ctas;
   oproj_dev::oproj_cta(
-      gp, dyn_smem, (int)blockIdx.x - fp.exchange_ctas, 0, threadIdx.x,
+      gp, dyn_smem, gidx / gp.splits, gidx % gp.splits, threadIdx.x,
       [] { named_barrier(kGemmBarrier, oproj_dev::kThreads); },
       [&](unsigned long long deadline) {
         // rows written by the combine warps (generic proxy, other SMs) must be complete before TMA reads them
@@ -126,7 +127,8 @@ cudaError_t launch_exchange_oproj(FusedParams fp, int channel_override, bool pdl
   if (E <= 0) return cudaSuccess;
   if (p.mode != kModeCombine || p.ranks_in_launch < 1 || p.ranks_in_launch > kFusedMaxRanks) return cudaErrorInvalidValue;
   for (int r = 0; r < p.ranks_in_launch; ++r)
-    if (fp.gemm[r].splits != 1) return cudaErrorInvalidValue;
+    if (fp.gemm[r].splits < 1 || (fp.gemm[r].splits > 1 && (fp.gemm[r].partial == nullptr || p.ranks_in_launch > 1)))
+      return cudaErrorInvalidValue;
   LaunchInfo li = plan_launch(p, channel_override);
   FusedFn fn = nullptr;
   int nit = 0;
@@ -147,7 +149,7 @@ cudaError_t launch_exchange_oproj(FusedParams fp, int channel_override, bool pdl
   e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, std::max(threads, 128), smem);
   if (e != cudaSuccess) return e;
   const int capacity = per_sm * sms / p.ranks_in_launch;     // CTAs one rank may use
-  const int gemm_ctas = fp.gemm[0].hidden / 128;
+  const int gemm_ctas = fp.gemm[0].hidden / 128 * fp.gemm[0].splits;
   if (capacity - gemm_ctas < 1) return cudaErrorNotSupported;
   li.channels = std::min(li.channels, capacity - gemm_ctas);
 

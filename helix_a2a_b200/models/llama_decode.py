@@ -50,7 +50,7 @@ class HelixDecodeStack:
 
     def __init__(self, cfg: LlamaDecodeConfig, *, batch: int, local_ctx: int, cp_size: int = 1, cp_rank: int = 0,
                  group: Optional[dist.ProcessGroup] = None, device="cuda", seed: int = 0,
-                 workspace: Optional[torch.Tensor] = None, kv_std: float = 1.0, fuse_oproj: bool = True):
+                 workspace: Optional[torch.Tensor] = None, kv_std: float = 1.0, fuse_oproj: bool = False):
         assert cfg.n_q_heads % cp_size == 0, "query heads must divide evenly over the CP ranks"
         self.cfg, self.batch, self.local_ctx = cfg, batch, local_ctx
         self.cp_size, self.cp_rank, self.group = cp_size, cp_rank, group
