@@ -2,7 +2,7 @@
 """Per-kernel timings on one GPU: decode attention and o_proj at the shapes of the headline
 benchmark, as achieved HBM bandwidth and fraction of the measured copy bandwidth.
 
-    python benchmarks/kernel_bench.py [--iters 20] [--json gpurun_out/kernels.json]
+    python benchmarks/kernel_bench.py [--iters 20] [--json results/kernels.json]
 
 Every timed launch reads buffers that were last touched several launches ago and that are together
 much larger than L2 (layers are rotated), CUDA events on the launching stream, >= 3 warm-ups.

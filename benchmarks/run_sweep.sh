@@ -4,13 +4,13 @@
 # FORCE=true (the reference's SLURM drivers resume the same way,
 # benchmark/sbatch/run_gb200_aiperf_v3.sbatch:307-311).  DRY_RUN=true only prints the plan.
 #
-#   CP_DEGREES="2 4 8" TOKENS="1,8,32,128,256" MODE=graph OUT=gpurun_out/sweep benchmarks/run_sweep.sh
+#   CP_DEGREES="2 4 8" TOKENS="1,8,32,128,256" MODE=graph OUT=results/sweep benchmarks/run_sweep.sh
 set -u
 cd "$(dirname "$0")/.."
 CP_DEGREES=${CP_DEGREES:-"2 4 8"}
 TOKENS=${TOKENS:-"1,8,32,128,256"}
 MODE=${MODE:-graph}
-OUT=${OUT:-gpurun_out/sweep}
+OUT=${OUT:-results/sweep}
 FORCE=${FORCE:-false}
 DRY_RUN=${DRY_RUN:-false}
 STEPS=${STEPS:-5}

@@ -473,8 +473,10 @@ __global__ void __launch_bounds__(kWarps * 32, 2) gqa_decode_kernel(const __grid
     }
   }
   if (p.trace != nullptr && threadIdx.x == 0) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
     p.trace[blockIdx.x * 4 + 0] = t_entry;
-    p.trace[blockIdx.x * 4 + 1] = t_first;
+    p.trace[blockIdx.x * 4 + 1] = (t_first << 8) | (unsigned long long)(smid & 0xffu);   // low byte: SM id
     p.trace[blockIdx.x * 4 + 2] = t_stream;
     p.trace[blockIdx.x * 4 + 3] = now_ns();
   }
