@@ -10,6 +10,7 @@
 #include <torch/extension.h>
 
 #include <cstdlib>
+#include <limits>
 #include <string>
 
 #include "exchange.h"
@@ -35,6 +36,12 @@ unsigned long long timeout_ns(int64_t timeout_ms) {
 }
 
 helix::LaunchInfo g_last_launch{};
+
+// HELIX_A2A_DEBUG=1: outputs are pre-filled with NaN so that a row the kernel failed to write shows up
+bool env_debug() {
+  const char* v = std::getenv("HELIX_A2A_DEBUG");
+  return v && v[0] == '1';
+}
 
 void check_cuda(cudaError_t e, const char* what) {
   TORCH_CHECK(e == cudaSuccess, "helix: ", what, " failed: ", cudaGetErrorString(e));
@@ -116,6 +123,10 @@ std::tuple<torch::Tensor, torch::Tensor> alltoall_impl(torch::Tensor partial_o, 
   for (int i = lead; i < partial_o.dim() - 2; i++) entries *= partial_o.size(i);
   torch::Tensor o_out = torch::empty_like(partial_o);
   torch::Tensor s_out = torch::empty_like(softmax_stats);
+  if (env_debug()) {
+    o_out.fill_(std::numeric_limits<float>::quiet_NaN());
+    s_out.fill_(std::numeric_limits<float>::quiet_NaN());
+  }
   if (entries == 0) return std::make_tuple(o_out, s_out);
   TORCH_CHECK(entries < (int64_t(1) << 30), "too many entries");
 
@@ -228,6 +239,7 @@ std::tuple<torch::Tensor, torch::Tensor> alltoall_combine(torch::Tensor attn_out
     in_o_rank_bytes = entries * cp_size * D * es; in_s_rank_bytes = entries * cp_size * 8;
     out_rank_bytes = entries * D * es; lse_rank_bytes = entries * 4;
   }
+  if (env_debug()) out.fill_(std::numeric_limits<float>::quiet_NaN());
   if ((int64_t)p.outer * p.inner == 0) return std::make_tuple(out, lse_out);
   for (int r = 0; r < ranks; ++r) {
     p.io[r].o_src = reinterpret_cast<const uint8_t*>(attn_out.data_ptr()) + r * in_o_rank_bytes;

@@ -23,6 +23,7 @@ import torch.distributed as dist
 from .ops import reference_math as rm
 from .parallel import cpu_backend, workspace as ws_mod
 from .parallel.workspace import CpuWorkspace
+from .utils.tracing import check_written, nvtx_range
 
 logger = logging.getLogger(__name__)
 
@@ -120,7 +121,10 @@ def alltoall(partial_o: torch.Tensor, softmax_stats: torch.Tensor, workspace: to
     if isinstance(workspace, CpuWorkspace):
         return cpu_backend.alltoall(partial_o, softmax_stats, workspace._helix_group, cp_size)
     from .ops._ext import ops
-    return ops().alltoall_helix_native(partial_o, softmax_stats, workspace, cp_rank, cp_size)
+    with nvtx_range("helix.alltoall"):
+        ro, rs = ops().alltoall_helix_native(partial_o, softmax_stats, workspace, cp_rank, cp_size)
+    check_written(ro, "alltoall output")
+    return ro, rs
 
 
 _STATS_MODES = {"lse": 0, "max_sumexp": 1}
@@ -154,9 +158,11 @@ def alltoall_combine(attn_out: torch.Tensor, lse: torch.Tensor, workspace: torch
         # nothing to exchange or combine
         return (attn_out, lse) if return_lse else attn_out
     from .ops._ext import ops
-    out, glse = ops().alltoall_combine(attn_out, lse, workspace, cp_rank, cp_size,
-                                       0 if layout == "native" else 1, return_lse, base2,
-                                       _STATS_MODES[stats_mode], False, 0, timeout_ms)
+    with nvtx_range("helix.alltoall_combine"):
+        out, glse = ops().alltoall_combine(attn_out, lse, workspace, cp_rank, cp_size,
+                                           0 if layout == "native" else 1, return_lse, base2,
+                                           _STATS_MODES[stats_mode], False, 0, timeout_ms)
+    check_written(out, "alltoall_combine output")
     return (out, glse) if return_lse else out
 
 

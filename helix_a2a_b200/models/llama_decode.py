@@ -22,6 +22,7 @@ import torch.distributed as dist
 
 from .. import api
 from ..ops import attention, oproj as oproj_mod
+from ..utils.tracing import nvtx_range
 
 
 @dataclass
@@ -93,9 +94,9 @@ class HelixDecodeStack:
 
     # ---- one layer / one step --------------------------------------------------------------------
     def layer(self, l: int, q: torch.Tensor) -> torch.Tensor:
-        cfg = self.cfg
-        o, lse = attention.gqa_decode(q, self.k_cache[l], self.v_cache[l], self.block_table, self.seq_lens,
-                                      scale=self.scale, max_seq_len=self.local_ctx)
+        with nvtx_range(f"layer{l}.attention"):
+            o, lse = attention.gqa_decode(q, self.k_cache[l], self.v_cache[l], self.block_table, self.seq_lens,
+                                          scale=self.scale, max_seq_len=self.local_ctx)
         if self.cp_size > 1 and self.fuse_oproj:
             # exchange + combine + o_proj in one launch: W_o streams while the exchange is in flight
             return api.alltoall_combine_oproj(o, lse, self.w_o[l], self.workspace, self.cp_rank, self.cp_size)

@@ -65,6 +65,13 @@ def main(argv=None) -> int:
         shutil.copy2(target, backup)
     with open(target, "w") as f:
         f.write(SHIM)
+    # The reference's installer also rewrites FlashAttentionImpl._dcp_fa_out of its vLLM fork so that the
+    # pre-allocated output buffer is sliced to the local head count (install_in_container.sh:56-97).
+    # Stock vLLM has no such method; say so instead of patching blindly.
+    fa = os.path.join(vdir, "v1", "attention", "backends", "flash_attn.py")
+    if os.path.exists(fa) and "def _dcp_fa_out" in open(fa).read():
+        print("note: this vLLM defines _dcp_fa_out (a fork); with attention-TP < TP its output buffer must be "
+              "sliced to the local head count before it reaches dcp_a2a_lse_reduce")
     print("installed; select the kernel with HELIX_A2A_BACKEND=native")
     return 0
 

@@ -165,6 +165,17 @@ def main():
     hb = hook.dcp_a2a_lse_reduce(o_in, l_in * 1.4426950408889634, _G, is_lse_base_on_e=False)
     check("vLLM hook, base-2 LSE", (hb.float() - wv[rank]).abs().max().item() < 2e-2)
 
+    # backend parity (the reference's end-to-end check compares greedy completions between the nccl and
+    # native backends, benchmark/scripts/correctness_check.sh:231-283): same hook, both backends, then the
+    # arg-max over the o_proj output must agree token for token
+    w_par = (torch.randn(512, (64 // world) * 128, device="cuda", generator=torch.Generator(device="cuda").manual_seed(9)) * 0.05).bfloat16()
+    hook._HELIX_BACKEND = "nccl"
+    y_nccl = torch.nn.functional.linear(hook.dcp_a2a_lse_reduce(o_in, l_in, _G).reshape(o_in.shape[0], -1).float(), w_par.float())
+    hook._HELIX_BACKEND = "native"
+    y_nat = torch.nn.functional.linear(hook.dcp_a2a_lse_reduce(o_in, l_in, _G).reshape(o_in.shape[0], -1).float(), w_par.float())
+    check("nccl and native backends agree (values and arg-max)",
+          (y_nccl - y_nat).abs().max().item() < 5e-2 and torch.equal(y_nccl.argmax(-1), y_nat.argmax(-1)))
+
     st_ = helix.check_status(ws, rank, world, raise_on_error=False)
     check("status clean", st_["code"] == 0)
 

@@ -261,3 +261,22 @@ def test_fused_exchange_combine_oproj(helix, cp, B, H, D, hidden):
             assert (y[r].float() - ref).abs().max() < 3e-2 * max(1.0, ref.abs().max().item()), (it, r)
     for r in range(cp):
         assert helix.check_status(ws, r, cp)["code"] == 0
+
+
+def test_debug_mode_poison_and_nvtx(helix):
+    """HELIX_A2A_DEBUG=1 pre-fills outputs with NaN and verifies every row was written; NVTX ranges are harmless."""
+    cp = 2
+    ws = _ws(helix, 1)
+    o = torch.randn(5, 1, 128, device="cuda").bfloat16()
+    s = torch.randn(5, 1, 2, device="cuda")
+    os.environ["HELIX_A2A_DEBUG"] = "1"
+    os.environ["HELIX_A2A_NVTX"] = "1"
+    try:
+        ro, rs = helix.alltoall(o, s, ws, 0, 1)
+        assert torch.equal(ro, o) and torch.equal(rs, s)
+        from helix_a2a_b200.utils.tracing import check_written
+        with pytest.raises(RuntimeError):
+            check_written(torch.full((2, 2), float("nan"), device="cuda"), "poisoned tensor")
+    finally:
+        del os.environ["HELIX_A2A_DEBUG"], os.environ["HELIX_A2A_NVTX"]
+    del cp
