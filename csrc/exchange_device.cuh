@@ -478,51 +478,17 @@ HELIX_D void receiver_combine_warp(const ExchangeParams& p, const Ctx& cx, const
         float l = ingest_lse(__shfl_sync(kFull, lo[0], 0), p.stats_mode, p.base2);
         acc.template add<BF16>(l, lo, hi);
       }
-      // Peers are visited in batches: the lines of up to PB peers are requested back to back (their
-      // L2 round trips overlap) and only a peer whose lines have not all landed yet is polled again.
-      constexpr int PB = NIT <= 3 ? 4 : (NIT <= 5 ? 2 : 1);
-      for (int jb = k; jb < N - 1 && alive; jb += G * PB) {
-        uint64_t blo[PB][NIT], bhi[PB][NIT];
-#pragma unroll
-        for (int pb = 0; pb < PB; ++pb) {
-          const int j = jb + pb * G;
-          if (j < N - 1) {
-            const int peer = (rank + N - 1 - j) % N;
-            const uint64_t q0 = __shfl_sync(kFull, rtail0, peer) + (uint64_t)i * L;
-            const uint8_t* ring = cx.my_row + ring_offset(cx.lay, peer, c);
-#pragma unroll
-            for (int it = 0; it < NIT; ++it) {
-              blo[pb][it] = bhi[pb][it] = 0ull;
-              const int ch = it * 32 + lane;
-              if (ch < nchunks) ld_volatile_16(ring + ll128::chunk_ring_offset(q0, ch), blo[pb][it], bhi[pb][it]);
-            }
-          }
+      for (int j = k; j < N - 1; j += G) {
+        const int peer = (rank + N - 1 - j) % N;
+        const uint64_t q0 = __shfl_sync(kFull, rtail0, peer) + (uint64_t)i * L;
+        const uint8_t* ring = cx.my_row + ring_offset(cx.lay, peer, c);
+        if (!poll_message<NIT>(cx, ring, q0, 0, nchunks, lane, lo, hi)) {
+          if (lane == 0) report(cx, kTimeoutRecv, peer, e);
+          alive = false;
+          break;
         }
-#pragma unroll
-        for (int pb = 0; pb < PB; ++pb) {
-          const int j = jb + pb * G;
-          if (j < N - 1 && alive) {
-            const int peer = (rank + N - 1 - j) % N;
-            const uint64_t q0 = __shfl_sync(kFull, rtail0, peer) + (uint64_t)i * L;
-            bool bad = false;
-#pragma unroll
-            for (int it = 0; it < NIT; ++it) {
-              const int ch = it * 32 + lane;
-              if (ch < nchunks && (ch & 7) == 7) bad |= (bhi[pb][it] != ll128::flag_of(q0 + (uint64_t)(ch >> 3)));
-            }
-            if (__any_sync(kFull, bad)) {
-              const uint8_t* ring = cx.my_row + ring_offset(cx.lay, peer, c);
-              if (!poll_message<NIT>(cx, ring, q0, 0, nchunks, lane, blo[pb], bhi[pb])) {
-                if (lane == 0) report(cx, kTimeoutRecv, peer, e);
-                alive = false;
-              }
-            }
-            if (alive) {
-              float l = ingest_lse(__shfl_sync(kFull, blo[pb][0], 0), p.stats_mode, p.base2);
-              acc.template add<BF16>(l, blo[pb], bhi[pb]);
-            }
-          }
-        }
+        float l = ingest_lse(__shfl_sync(kFull, lo[0], 0), p.stats_mode, p.base2);
+        acc.template add<BF16>(l, lo, hi);
       }
     }
     if (G > 1) {
