@@ -23,19 +23,18 @@ struct GqaDecodeParams {
   const int32_t* seq_lens;     // [B] tokens of the LOCAL KV shard
   __nv_bfloat16* o;            // [B, Hq, 128]
   float* lse;                  // [B, Hq]
-  float* part_o;               // scratch [chunks, 2, 8, 128] fp32: two partial slots per chunk
-  float* part_lse;             // scratch [chunks, 2, 8]
+  float* part_o;               // scratch [ctas, 2, 8, 128] fp32: two partial slots per CTA
+  float* part_lse;             // scratch [ctas, 2, 8]
   int* counters;               // scratch [B * Hkv], zero on entry, zero again on exit
   int* error_flag;             // set to a helix::Status code when a bounded wait runs out
   unsigned long long* trace;   // optional [ctas][4] %globaltimer stamps: entry, first data, end of streaming, exit
-  int* work_counter;           // scratch [2], zero on entry and on exit: next chunk to hand out, CTAs that left
-  int B, Hq, Hkv, page_size, ctas, chunks;   // chunks >= ctas
+  int B, Hq, Hkv, page_size, ctas;
   float scale;
   int lse_base2;
   unsigned long long timeout_ns;
 };
 
-constexpr int kGqaMaxCtas = 640;   // upper bound of the chunk count (and of the pieces one pair can be cut into)
+constexpr int kGqaMaxCtas = 640;   // upper bound of the grid (and of the pieces one pair can be cut into)
 
 // scratch sizes (independent of the batch: two partial slots per CTA)
 inline size_t gqa_part_o_floats(int ctas) { return (size_t)ctas * 2 * 8 * 128; }
@@ -43,7 +42,6 @@ inline size_t gqa_part_lse_floats(int ctas) { return (size_t)ctas * 2 * 8; }
 
 // number of CTAs that fills the device for this batch (two per SM unless the work is tiny)
 int gqa_pick_ctas(int B, int Hkv, int max_seq_len, int sm_count);
-int gqa_pick_chunks(int B, int Hkv, int max_seq_len, int ctas);
 
 cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t stream);
 

@@ -126,16 +126,10 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   c10::cuda::CUDAGuard guard(q.device());
   auto stream = at::cuda::getCurrentCUDAStream();
 
-  // splits > 0 asks for about that many chunks per (sequence, kv head) pair; 0 lets the library choose
-  const int msl = (int)std::max<int64_t>(max_seq_len, 1);
-  int nctas, sp;
-  if (splits > 0) {
-    sp = (int)std::max<int64_t>(std::min<int64_t>((int64_t)B * Hkv * splits, helix::kGqaMaxCtas), 1);
-    nctas = std::min(sp, 2 * helix::device_sm_count());
-  } else {
-    nctas = std::max(helix::gqa_pick_ctas(B, Hkv, msl, helix::device_sm_count()), 1);
-    sp = helix::gqa_pick_chunks(B, Hkv, msl, nctas);
-  }
+  // splits > 0 asks for about that many CTAs per (sequence, kv head) pair; 0 lets the library choose
+  int sp = splits > 0 ? (int)std::min<int64_t>((int64_t)B * Hkv * splits, helix::kGqaMaxCtas)
+                      : helix::gqa_pick_ctas(B, Hkv, (int)std::max<int64_t>(max_seq_len, 1), helix::device_sm_count());
+  sp = std::max(sp, 1);
   torch::Tensor o = torch::empty({B, Hq, 128}, q.options());
   torch::Tensor lse = torch::empty({B, Hq}, q.options().dtype(torch::kFloat32));
   if (B == 0) return std::make_tuple(o, lse);
@@ -156,8 +150,7 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   p.part_lse = sc.part_b.data_ptr<float>();
   p.counters = sc.counters.data_ptr<int32_t>();
   p.error_flag = sc.error_flag.data_ptr<int32_t>();
-  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page; p.ctas = nctas; p.chunks = sp;
-  p.work_counter = sc.counters.data_ptr<int32_t>() + (sc.counters.numel() - 512);
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page; p.ctas = sp;
   p.scale = (float)scale;
   p.lse_base2 = lse_base2 ? 1 : 0;
   p.timeout_ns = env_timeout_ns();

@@ -3,9 +3,8 @@
 // Decode attention is bound by streaming the KV cache from HBM once.  The kernel is organised
 // around that stream:
 //   * balanced partition: the 16-token KV blocks of all (sequence, kv head) pairs form one linear
-//     index space that is cut into equal contiguous chunks, about two per CTA (two CTAs per SM);
-//     a CTA starts with its own chunk and draws the following ones from a global counter, so the
-//     load is even whatever the batch size, the sequence lengths or the SMs' distance to HBM; a
+//     index space that is cut into gridDim.x equal contiguous chunks (two CTAs per SM), so every
+//     CTA streams the same number of bytes whatever the batch size or the sequence lengths; a
 //     chunk may end one pair and begin the next;
 //   * every warp of a CTA owns its own 3-stage ring of KV blocks in shared memory and walks blocks
 //     warp, warp + W, ... of the CTA's segment, so warps never synchronise while streaming;
@@ -97,15 +96,9 @@ __global__ void __launch_bounds__(kWarps * 32, 2) gqa_decode_kernel(const __grid
     for (int b = 512; b < p.B; ++b) total += blocks_of(p.seq_lens[b]);
     total *= Hkv;
   }
-  // The block space is cut into p.chunks equal chunks (more chunks than CTAs).  CTA i starts with
-  // chunk i and then draws further chunks from a global counter, so SMs that stream faster (HBM
-  // distance differs between SMs) simply take more of them.
-  const long long chunk = max((total + p.chunks - 1) / (long long)p.chunks, 1LL);
-  __shared__ int s_next_chunk[2];
-  int cur_chunk = blockIdx.x, chunk_parity = 0;
-  long long g0 = (long long)cur_chunk * chunk;
-  long long g1 = min(total, g0 + chunk);
-  if (threadIdx.x == 0) s_next_chunk[0] = (int)gridDim.x + atomicAdd(&p.work_counter[0], 1);
+  const long long chunk = max((total + gridDim.x - 1) / (long long)gridDim.x, 1LL);
+  const long long g0 = (long long)blockIdx.x * chunk;
+  const long long g1 = min(total, g0 + chunk);
 
   uint8_t* my_smem = smem + warp * (kStages * kStageBytes);
   const float sl2 = p.scale * kLog2e;
@@ -117,42 +110,22 @@ __global__ void __launch_bounds__(kWarps * 32, 2) gqa_decode_kernel(const __grid
 
   // ---- segment cursor: a segment is the part of one (sequence, kv head) pair inside [g0, g1) ----
   struct Seg {
-    int b, kvh, kb_begin, kb_end, n_blocks, seq_len, chunk;
+    int b, kvh, kb_begin, kb_end, n_blocks, seq_len;
     long long pair_start;
     bool valid;
   };
   int cur_b = 0;
   long long base = 0;        // global index of block 0 of (cur_b, kvh = 0)
+  while (cur_b < p.B) {
+    const long long span = (long long)blocks_of(p.seq_lens[cur_b]) * Hkv;
+    if (g0 < base + span) break;
+    base += span;
+    ++cur_b;
+  }
   long long gcur = g0;
-  auto seek = [&]() {        // position (cur_b, base) on the sequence that contains g0
-    cur_b = 0;
-    base = 0;
-    while (cur_b < p.B) {
-      const long long span = (long long)blocks_of(p.seq_lens[cur_b]) * Hkv;
-      if (g0 < base + span) break;
-      base += span;
-      ++cur_b;
-    }
-    gcur = g0;
-  };
-  seek();
   auto next_segment = [&]() {
     Seg sg;
     sg.valid = false;
-    if (gcur >= g1 && g0 < total) {
-      // this chunk is done: move on to the chunk drawn when it was entered (the draw was published
-      // to shared memory at least one CTA barrier ago) and draw the one after it
-      const int nxt = s_next_chunk[chunk_parity];
-      if (nxt < p.chunks) {
-        cur_chunk = nxt;
-        chunk_parity ^= 1;
-        g0 = (long long)cur_chunk * chunk;
-        g1 = min(total, g0 + chunk);
-        if (threadIdx.x == 0) s_next_chunk[chunk_parity] = (int)gridDim.x + atomicAdd(&p.work_counter[0], 1);
-        seek();
-      }
-    }
-    sg.chunk = cur_chunk;
     while (gcur < g1 && cur_b < p.B) {
       const int seq_len = p.seq_lens[cur_b];
       const int n_blocks = blocks_of(seq_len);
@@ -335,8 +308,8 @@ __global__ void __launch_bounds__(kWarps * 32, 2) gqa_decode_kernel(const __grid
 
     // ---- merge the warps' partials, four heads per round -------------------------------------------
     const int slot = (kb_begin == 0) ? 1 : 0;   // slot 1: the piece that starts its pair, slot 0: a continuation
-    float* part_o = p.part_o + ((size_t)(cur.chunk * 2 + slot) * 8) * kD;
-    float* part_l = p.part_lse + (size_t)(cur.chunk * 2 + slot) * 8;
+    float* part_o = p.part_o + ((size_t)(blockIdx.x * 2 + slot) * 8) * kD;
+    float* part_l = p.part_lse + (size_t)(blockIdx.x * 2 + slot) * 8;
     if (t == 0) {
       s_m[warp][g] = m_run;
       s_l[warp][g] = l_run;
@@ -465,13 +438,6 @@ __global__ void __launch_bounds__(kWarps * 32, 2) gqa_decode_kernel(const __grid
     }
   }
 
-  // the last CTA to leave re-arms the chunk counter for the next launch
-  if (threadIdx.x == 0) {
-    if (atomicAdd(&p.work_counter[1], 1) == (int)gridDim.x - 1) {
-      p.work_counter[0] = 0;
-      p.work_counter[1] = 0;
-    }
-  }
   if (p.trace != nullptr && threadIdx.x == 0) {
     unsigned smid;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
@@ -503,15 +469,9 @@ int gqa_pick_ctas(int B, int Hkv, int max_seq_len, int sm_count) {
   return (int)std::min<long long>(ctas, kGqaMaxCtas);
 }
 
-// Chunks the block space is cut into.  One per CTA by default: with only two or three chunks per
-// CTA the dynamic hand-out lengthens the tail (a CTA that draws its last chunk late runs it alone;
-// measured 100 -> 118 us at batch 8 x 16K tokens), and finer chunks pay the per-chunk ramp and
-// merge too often.  Callers can still ask for more chunks than CTAs.
-int gqa_pick_chunks(int /*B*/, int /*Hkv*/, int /*max_seq_len*/, int ctas) { return std::min(ctas, kGqaMaxCtas); }
-
 cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t stream) {
   if (p.B <= 0) return cudaSuccess;
-  if (p.Hq % p.Hkv != 0 || p.Hq / p.Hkv > 8 || p.page_size % kBlockTok != 0 || p.ctas < 1 || p.chunks < p.ctas || p.chunks > kGqaMaxCtas)
+  if (p.Hq % p.Hkv != 0 || p.Hq / p.Hkv > 8 || p.page_size % kBlockTok != 0 || p.ctas < 1 || p.ctas > kGqaMaxCtas)
     return cudaErrorInvalidValue;
   static bool attr_set[64] = {false};
   int dev = 0;

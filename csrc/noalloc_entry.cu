@@ -7,7 +7,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
-#include <algorithm>
 #include <cstdio>
 #include <mutex>
 
@@ -21,7 +20,7 @@ namespace {
 //   [0, kPartO)                    partial outputs   [MAX_CTAS][2][8][128] fp32
 //   [kPartO, kPartO + kPartL)      partial LSEs      [MAX_CTAS][2][8]      fp32
 //   then                           arrival counters  [MAX_PAIRS]           int32   (must be zero at launch)
-//   then                           error word        int32, chunk counters int32[2] at +64 (must be zero at launch)
+//   then                           error word        int32 (+ padding)             (must be zero at launch)
 constexpr size_t kPartO = (size_t)HELIX_NOALLOC_MAX_CTAS * 2 * 8 * 128 * sizeof(float);
 constexpr size_t kPartL = (size_t)HELIX_NOALLOC_MAX_CTAS * 2 * 8 * sizeof(float);
 constexpr size_t kCounters = (size_t)HELIX_NOALLOC_MAX_PAIRS * sizeof(int);
@@ -138,15 +137,13 @@ extern "C" __attribute__((visibility("default"))) int helix_gqa_decode_noalloc(
   p.Hkv = kv_heads;
   p.page_size = page_size;
   p.ctas = ctas;
-  p.chunks = std::min(helix::gqa_pick_chunks(batch, kv_heads, max_seq_len > 0 ? max_seq_len : 1, ctas), (int)HELIX_NOALLOC_MAX_CTAS);
-  p.work_counter = p.error_flag + 16;
   p.scale = scale;
   p.lse_base2 = lse_base2 ? 1 : 0;
   p.timeout_ns = 2000000000ull;
   // the array keeps the previous call's contents: counters and the error word must start at zero
   cudaError_t e = cudaMemsetAsync(p.counters, 0, (size_t)batch * kv_heads * sizeof(int), s);
   if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(counters)");
-  e = cudaMemsetAsync(p.error_flag, 0, kErr, s);
+  e = cudaMemsetAsync(p.error_flag, 0, sizeof(int), s);
   if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(error word)");
   e = helix::launch_gqa_decode(p, false, s);
   if (e != cudaSuccess) return fail_cuda(e, "kernel launch");

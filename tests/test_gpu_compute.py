@@ -29,7 +29,7 @@ def _paged_case(B, Hq, Hkv, seq_lens, page=16, layout="HND", seed=0):
 
 @pytest.mark.parametrize("layout", ["HND", "NHD"])
 @pytest.mark.parametrize("seq_lens,splits", [([5], 1), ([16, 17, 300], 1), ([1000, 37, 512, 2048], 3),
-                                             ([4096, 4000], 0), ([129] * 5, 4), ([2048] * 5, 16)])
+                                             ([4096, 4000], 0), ([129] * 5, 4)])
 def test_gqa_decode_matches_fp32_reference(built, layout, seq_lens, splits):
     from helix_a2a_b200.ops import attention, reference_math as rm
     from helix_a2a_b200.ops.oproj import check_compute_status
