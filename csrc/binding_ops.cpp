@@ -34,7 +34,7 @@ struct Scratch {
   torch::Tensor error_flag;    // int32 [1]
   torch::Tensor counters;      // int32 [N]
   torch::Tensor part_a, part_b;  // float32 pools
-  torch::Tensor trace;           // int64 [kGqaMaxCtas * 4], only with HELIX_A2A_ATTN_TRACE=1
+  torch::Tensor trace;           // int64 [kGqaMaxCtas * 4], only with HELIX_A2A_ATTN_TRACE=1 / HELIX_A2A_OPROJ_TRACE=1
 };
 std::mutex g_mu;
 std::map<int, Scratch> g_scratch;
@@ -244,8 +244,19 @@ torch::Tensor oproj(torch::Tensor x, torch::Tensor w, int64_t splits) {
     torch::Tensor xs = x.narrow(0, t0, nt);
     const int n_pad = (nt + 15) / 16 * 16;
     int sp = (int)splits;
-    if (sp <= 0) sp = helix::oproj_pick_splits(hidden, K, helix::device_sm_count());
-    Scratch& sc = scratch_for(x.device(), hidden / 128 + 1024, sp > 1 ? (int64_t)helix::oproj_partial_bytes(hidden, sp, n_pad) / 4 : 0, 0);
+    const int sms = helix::device_sm_count();
+    // splits: 0 = pick (stream-K when it pays), -1 = force stream-K, >= 1 = that many K splits
+    bool streamk = sp == -1 || (sp == 0 && helix::oproj_streamk_pays(hidden, K, n_pad, sms));
+    if (sp == 0) {
+      // HELIX_A2A_OPROJ_STREAMK=1 / 0 overrides the choice for calls that leave it to the library
+      if (const char* v = std::getenv("HELIX_A2A_OPROJ_STREAMK")) streamk = std::string(v) == "1";
+    }
+    const int bk = 64 * helix::oproj_pick_atoms(n_pad);
+    const int sk_ctas = (int)std::min<int64_t>(sms, (int64_t)(hidden / 128) * ((K + bk - 1) / bk));
+    if (sp <= 0) sp = helix::oproj_pick_splits(hidden, K, sms);
+    const int64_t part_floats = streamk ? (int64_t)helix::oproj_streamk_partial_floats(sk_ctas, n_pad)
+                                        : (sp > 1 ? (int64_t)helix::oproj_partial_bytes(hidden, sp, n_pad) / 4 : 0);
+    Scratch& sc = scratch_for(x.device(), hidden / 128 + 1024, part_floats, 0);
     helix::OprojParams p{};
     p.w_map = mat_map(w, 128);
     p.x_map = mat_map(xs, n_pad);
@@ -259,14 +270,24 @@ torch::Tensor oproj(torch::Tensor x, torch::Tensor w, int64_t splits) {
     p.stages = helix::oproj_pick_stages(n_pad);
     p.atoms = helix::oproj_pick_atoms(n_pad);
     p.timeout_ns = env_timeout_ns();
-    check_cuda(helix::launch_oproj(p, env_pdl(), stream), "o_proj launch");
+    p.ctas = sk_ctas;
+    p.trace = nullptr;
+    if (streamk) {
+      static const bool trace_on = [] { const char* v = std::getenv("HELIX_A2A_OPROJ_TRACE"); return v && std::string(v) == "1"; }();
+      if (trace_on) {
+        if (!sc.trace.defined()) sc.trace = torch::zeros({helix::kGqaMaxCtas * 4}, x.options().dtype(torch::kInt64));
+        p.trace = reinterpret_cast<unsigned long long*>(sc.trace.data_ptr());
+      }
+    }
+    check_cuda(streamk ? helix::launch_oproj_streamk(p, env_pdl(), stream) : helix::launch_oproj(p, env_pdl(), stream),
+               "o_proj launch");
   }
   return y;
 }
 
 torch::Tensor attn_trace(torch::Tensor like) {
   Scratch& sc = scratch_for(like.device(), 1, 0, 0);
-  TORCH_CHECK(sc.trace.defined(), "no trace recorded: set HELIX_A2A_ATTN_TRACE=1");
+  TORCH_CHECK(sc.trace.defined(), "no trace recorded: set HELIX_A2A_ATTN_TRACE=1 (or HELIX_A2A_OPROJ_TRACE=1)");
   return sc.trace.clone();
 }
 

@@ -20,6 +20,9 @@ struct OprojParams {
   int* counters;         // scratch [m_tiles], zero on entry and on exit
   int* error_flag;
   int tokens, n_pad, hidden, K, splits, stages, atoms;   // atoms: 64-wide K atoms per stage (1, 2 or 4)
+  int ctas;              // stream-K variant only: CTAs of the launch (splits is ignored there)
+  unsigned long long* trace;   // stream-K variant, optional [ctas][8] %globaltimer stamps: entry, set-up done,
+                               // first stage landed, last MMA issued, accumulator complete, exit
   unsigned long long timeout_ns;
 };
 
@@ -32,5 +35,11 @@ int oproj_pick_atoms(int n_pad);
 int oproj_smem_bytes(int n_pad, int stages);
 
 cudaError_t launch_oproj(const OprojParams& p, bool pdl, cudaStream_t stream);
+
+// Stream-K variant: the (slab, k-block) units are dealt evenly to one CTA per SM, so every SM streams the same
+// share of W whatever hidden / 128 is.  Scratch: partial [ctas][2][n_pad][128] fp32, counters [hidden / 128].
+inline size_t oproj_streamk_partial_floats(int ctas, int n_pad) { return (size_t)ctas * 2 * n_pad * 128; }
+bool oproj_streamk_pays(int hidden, int K, int n_pad, int sm_count);
+cudaError_t launch_oproj_streamk(const OprojParams& p, bool pdl, cudaStream_t stream);
 
 }  // namespace helix

@@ -9,7 +9,11 @@ import torch
 
 
 def oproj(x: torch.Tensor, w: torch.Tensor, *, splits: int = 0) -> torch.Tensor:
-    """``x [tokens, K]`` bf16, ``w [hidden, K]`` bf16 (``nn.Linear`` weight layout) -> bf16 ``[tokens, hidden]``."""
+    """``x [tokens, K]`` bf16, ``w [hidden, K]`` bf16 (``nn.Linear`` weight layout) -> bf16 ``[tokens, hidden]``.
+
+    ``splits``: 0 lets the library pick (stream-K over all SMs when the plain grid would leave
+    some idle), -1 forces the stream-K kernel, ``n >= 1`` forces the plain kernel with ``n`` K splits.
+    """
     if not x.is_cuda:
         return (x.float() @ w.float().t()).to(x.dtype)
     from ._ext import ops

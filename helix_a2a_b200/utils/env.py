@@ -58,3 +58,14 @@ def handle_transport() -> str:
 
 def debug() -> bool:
     return os.environ.get("HELIX_A2A_DEBUG", "0").strip() in _TRUE
+
+
+def oproj_streamk() -> str:
+    """``HELIX_A2A_OPROJ_STREAMK``: ``1`` / ``0`` forces / forbids the stream-K o_proj kernel for calls
+    that leave the choice to the library; unset = the library's heuristic.  Read by the extension."""
+    return os.environ.get("HELIX_A2A_OPROJ_STREAMK", "auto").strip().lower()
+
+
+def oproj_trace() -> bool:
+    """``HELIX_A2A_OPROJ_TRACE=1``: the stream-K o_proj kernel records ``%globaltimer`` stamps per CTA."""
+    return os.environ.get("HELIX_A2A_OPROJ_TRACE", "0").strip() == "1"

@@ -58,7 +58,9 @@ def test_gqa_decode_small_group_base2_and_empty_sequence(built):
 
 
 @pytest.mark.parametrize("tokens", [1, 8, 17, 64, 200, 300])
-@pytest.mark.parametrize("hidden,K,splits", [(8192, 1024, 0), (1024, 8192, 1), (512, 256, 2), (8192, 8192, 0)])
+@pytest.mark.parametrize("hidden,K,splits", [(8192, 1024, 0), (1024, 8192, 1), (512, 256, 2), (8192, 8192, 0),
+                                             (8192, 8192, -1), (8192, 1024, -1), (512, 256, -1), (1152, 832, -1),
+                                             (1024, 8192, 3), (512, 4096, 8), (1024, 2048, 4)])
 def test_oproj_matches_fp32_matmul(built, tokens, hidden, K, splits):
     from helix_a2a_b200.ops.oproj import oproj, check_compute_status
     torch.manual_seed(tokens + hidden)
