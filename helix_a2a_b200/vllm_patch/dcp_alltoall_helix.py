@@ -8,8 +8,8 @@ module it replaces in vLLM 0.22 (``vllm/v1/attention/ops/dcp_alltoall.py``)::
     dcp_a2a_ensure_initialized(cp_group)     # before CUDA-graph capture
 
 Backend switch, read at import like the reference (``patches/dcp_alltoall_helix.py:40,49``):
-``HELIX_A2A_BACKEND=nccl`` (default) keeps the stock path — vLLM's own implementation when vLLM
-is importable, else two ``all_to_all_single`` + a torch combine; ``native`` runs ONE kernel that
+``HELIX_A2A_BACKEND=nccl`` (default) is two ``all_to_all_single`` + a torch combine
+(``HELIX_A2A_NCCL_IMPL=stock`` calls the function of the replaced vLLM module instead); ``native`` runs ONE kernel that
 reads ``cp_attn_out`` / ``cp_attn_lse`` in place (no permute / pad / zeros copies), exchanges over
 NVLink and applies the LSE-weighted combine on the receive side.  Base-2 LSEs (FlashInfer) are
 combined natively instead of being converted to base e and back
@@ -33,6 +33,9 @@ from helix_a2a_b200.ops import reference_math as _rm
 logger = logging.getLogger(__name__)
 
 _HELIX_BACKEND = os.environ.get("HELIX_A2A_BACKEND", "nccl").lower()
+# What "nccl" means: "own" = two all_to_all_single + a torch combine, as in the reference's hook
+# (patches/dcp_alltoall_helix.py:455-504); "stock" = the function of the vLLM module this hook replaced.
+_NCCL_IMPL = os.environ.get("HELIX_A2A_NCCL_IMPL", "own").lower()
 _workspace: Optional[torch.Tensor] = None
 _workspace_key = None
 _stock_reduce = None     # vLLM's original function, when it could be imported
@@ -123,7 +126,7 @@ def dcp_a2a_lse_reduce(cp_attn_out: torch.Tensor, cp_attn_lse: torch.Tensor, cp_
         lse = cp_attn_lse if cp_attn_lse.dtype == torch.float32 else cp_attn_lse.float()
         return _helix.alltoall_combine(cp_attn_out.contiguous(), lse.contiguous(), ws, rank, world,
                                        return_lse=return_lse, base2=not is_lse_base_on_e)
-    if _stock_reduce is not None:
+    if _stock_reduce is not None and _NCCL_IMPL == "stock":
         return _stock_reduce(cp_attn_out, cp_attn_lse, cp_group, ctx, return_lse, is_lse_base_on_e)
     return _nccl_reduce(cp_attn_out, cp_attn_lse, cp_group, return_lse, is_lse_base_on_e)
 
