@@ -31,6 +31,11 @@ struct GqaDecodeParams {
   int B, Hq, Hkv, page_size, ctas;
   float scale;
   int lse_base2;
+  // 1: the kernel before this one in the stream writes at most the newest token of each sequence (the cache
+  // append) and q; block_table, seq_lens and all older KV are already final.  Under programmatic launch the
+  // first K/V tiles are then requested before the wait on that kernel, except by a CTA whose first segment
+  // reaches the end of its sequence.
+  int kv_stable;
   unsigned long long timeout_ns;
 };
 

@@ -104,7 +104,7 @@ CUtensorMap mat_map(const torch::Tensor& t, int64_t box_rows) {
 // ---- GQA paged decode attention -----------------------------------------------------------------
 std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tensor k_cache, torch::Tensor v_cache,
                                                     torch::Tensor block_table, torch::Tensor seq_lens, double scale,
-                                                    bool lse_base2, bool hnd, int64_t splits, int64_t max_seq_len) {
+                                                    bool lse_base2, bool hnd, int64_t splits, int64_t max_seq_len, bool kv_stable) {
   TORCH_CHECK(q.is_cuda() && k_cache.is_cuda() && v_cache.is_cuda() && block_table.is_cuda() && seq_lens.is_cuda(),
               "all inputs must be on CUDA");
   TORCH_CHECK(q.scalar_type() == at::ScalarType::BFloat16 && k_cache.scalar_type() == at::ScalarType::BFloat16 &&
@@ -162,6 +162,7 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
       p.trace = reinterpret_cast<unsigned long long*>(sc.trace.data_ptr());
     }
   }
+  p.kv_stable = kv_stable ? 1 : 0;
   check_cuda(helix::launch_gqa_decode(p, env_pdl(), stream), "gqa decode launch");
   return std::make_tuple(o, lse);
 }
@@ -397,7 +398,7 @@ void clear_error_flag(torch::Tensor like) {
 void register_compute_ops(torch::Library& m) {
   m.def(
       "gqa_decode(Tensor q, Tensor k_cache, Tensor v_cache, Tensor block_table, Tensor seq_lens, float scale, bool "
-      "lse_base2, bool hnd, int splits, int max_seq_len) -> (Tensor, Tensor)",
+      "lse_base2, bool hnd, int splits, int max_seq_len, bool kv_stable=False) -> (Tensor, Tensor)",
       &gqa_decode);
   m.def(
       "mla_decode(Tensor q_nope, Tensor q_pe, Tensor ckv, Tensor scales, Tensor kpe, Tensor block_table, Tensor seq_lens, "

@@ -78,7 +78,8 @@ __global__ void __launch_bounds__(kWarps * 32, 2) gqa_decode_kernel(const __grid
     tma_prefetch_desc(&p.v_map);
   }
   __syncthreads();
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const bool early_kv = p.kv_stable != 0;
+  if (!early_kv) asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const unsigned long long t_entry = now_ns();
   const unsigned long long deadline = t_entry + p.timeout_ns;
@@ -181,7 +182,16 @@ __global__ void __launch_bounds__(kWarps * 32, 2) gqa_decode_kernel(const __grid
   float* s_o = reinterpret_cast<float*>(smem + kSmemPipe);   // [kWarps][4][kD]: merge buffer, not part of the rings
 
   Seg cur = next_segment();
-  if (cur.valid) prologue(cur);
+  if (early_kv) {
+    // old KV does not depend on the kernel before us: request the first tiles, then wait for it (q does depend).
+    // A segment that reaches the newest token waits first: that token's K/V row may still be on its way.
+    const bool touches_newest = cur.valid && cur.kb_end == cur.n_blocks;
+    if (touches_newest) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (cur.valid) prologue(cur);
+    if (!touches_newest) asm volatile("griddepcontrol.wait;" ::: "memory");
+  } else if (cur.valid) {
+    prologue(cur);
+  }
   while (cur.valid) {
     const int b = cur.b, kvh = cur.kvh, seq_len = cur.seq_len, n_blocks = cur.n_blocks;
     const int kb_begin = cur.kb_begin, kb_end = cur.kb_end;

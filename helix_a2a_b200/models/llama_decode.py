@@ -96,7 +96,7 @@ class HelixDecodeStack:
     def layer(self, l: int, q: torch.Tensor) -> torch.Tensor:
         with nvtx_range(f"layer{l}.attention"):
             o, lse = attention.gqa_decode(q, self.k_cache[l], self.v_cache[l], self.block_table, self.seq_lens,
-                                          scale=self.scale, max_seq_len=self.local_ctx)
+                                          scale=self.scale, max_seq_len=self.local_ctx, kv_stable=True)
         if self.cp_size > 1 and self.fuse_oproj:
             # exchange + combine + o_proj in one launch: W_o streams while the exchange is in flight
             return api.alltoall_combine_oproj(o, lse, self.w_o[l], self.workspace, self.cp_rank, self.cp_size)

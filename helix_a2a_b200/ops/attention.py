@@ -17,7 +17,8 @@ from . import reference_math as rm
 
 def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                seq_lens: torch.Tensor, *, scale: Optional[float] = None, lse_base2: bool = False,
-               layout: str = "HND", splits: int = 0, max_seq_len: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+               layout: str = "HND", splits: int = 0, max_seq_len: int = 0,
+               kv_stable: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Decode attention of ``q [B, Hq, 128]`` over each sequence's local KV pages.
 
     ``k_cache`` / ``v_cache``: ``[pages, Hkv, page, 128]`` (``layout="HND"``) or
@@ -25,6 +26,9 @@ def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bl
     ``seq_lens [B]`` int32 (tokens of the LOCAL shard).  Returns ``o [B, Hq, 128]`` (bf16,
     normalised) and ``lse [B, Hq]`` (fp32; natural log, or base 2 with ``lse_base2``).
     ``splits=0`` lets the library pick the number of KV splits from ``max_seq_len``.
+    ``kv_stable=True`` is a promise about the kernel launched just before this one on the stream: it
+    writes at most the newest token of each sequence (the cache append) and ``q``.  With
+    ``HELIX_A2A_ENABLE_PDL=1`` the first K/V tiles are then fetched while that kernel is still draining.
     """
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     if not q.is_cuda:
@@ -36,7 +40,7 @@ def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bl
     if max_seq_len <= 0:
         max_seq_len = block_table.shape[1] * (k_cache.shape[2] if layout == "HND" else k_cache.shape[1])
     return ops().gqa_decode(q, k_cache, v_cache, block_table, seq_lens, float(scale), lse_base2,
-                            layout == "HND", splits, max_seq_len)
+                            layout == "HND", splits, max_seq_len, kv_stable)
 
 
 def mla_decode(q_nope: torch.Tensor, q_pe: torch.Tensor, ckv_fp8: torch.Tensor, scales: torch.Tensor,

@@ -69,3 +69,14 @@ def oproj_streamk() -> str:
 def oproj_trace() -> bool:
     """``HELIX_A2A_OPROJ_TRACE=1``: the stream-K o_proj kernel records ``%globaltimer`` stamps per CTA."""
     return os.environ.get("HELIX_A2A_OPROJ_TRACE", "0").strip() == "1"
+
+
+def nccl_impl() -> str:
+    """``HELIX_A2A_NCCL_IMPL``: what ``HELIX_A2A_BACKEND=nccl`` runs inside the vLLM hook - ``own``
+    (default: two ``all_to_all_single`` + torch combine) or ``stock`` (the replaced vLLM function)."""
+    return os.environ.get("HELIX_A2A_NCCL_IMPL", "own").strip().lower()
+
+
+def vllm_hook_enabled() -> bool:
+    """``HELIX_A2A_VLLM_HOOK=0`` keeps the start-up shim (``vllm_patch/autoload``) from installing the import hook."""
+    return os.environ.get("HELIX_A2A_VLLM_HOOK", "1").strip() != "0"

@@ -45,6 +45,25 @@ def test_gqa_decode_matches_fp32_reference(built, layout, seq_lens, splits):
     assert (lse - lse_ref).abs().max() < 2e-3
 
 
+@pytest.mark.parametrize("seq_lens", [[8192, 300, 4096], [40000]])
+def test_gqa_decode_early_kv_prefetch_under_programmatic_launch(built, monkeypatch, seq_lens):
+    """kv_stable: K/V tiles are requested before the wait on the preceding kernel; q comes from that kernel."""
+    from helix_a2a_b200.ops import attention, reference_math as rm
+    from helix_a2a_b200.ops.oproj import check_compute_status
+    monkeypatch.setenv("HELIX_A2A_ENABLE_PDL", "1")
+    q0, kc, vc, bt, sl = _paged_case(len(seq_lens), 64, 8, seq_lens, seed=11)
+    big = torch.randn(64 << 20, device="cuda")
+    for _ in range(3):
+        big.mul_(1.0001)                       # keeps the GPU busy so that q's producer is still in flight
+        q = (q0.float() * 2.0).bfloat16()      # q is produced by the kernel right before the attention
+        o, lse = attention.gqa_decode(q, kc, vc, bt, sl, max_seq_len=max(seq_lens), kv_stable=True)
+    torch.cuda.synchronize()
+    check_compute_status(q)
+    o_ref, lse_ref = rm.paged_decode_attention_reference(q.float(), kc.float(), vc.float(), bt, sl, 1 / math.sqrt(128))
+    assert (o.float() - o_ref).abs().max() < 2e-2
+    assert (lse - lse_ref).abs().max() < 2e-3
+
+
 def test_gqa_decode_small_group_base2_and_empty_sequence(built):
     from helix_a2a_b200.ops import attention, reference_math as rm
     seq_lens = [0, 40, 16]
