@@ -67,6 +67,8 @@ struct MlaDecodeParams {
   float* part_lse;               // scratch [ctas, 2, 128]
   int* counters;                 // scratch [B], zero on entry and on exit
   int* error_flag;
+  unsigned long long* prof;      // optional [ctas][8] clock64 sums of thread 0: waits, dequantise, Q K^T, softmax (+ rescale),
+                                 // P store + P V issue, tiles, all clocks of the tile loop
   int B, page_size, ctas;
   float scale;
   int lse_base2;

@@ -221,6 +221,14 @@ std::tuple<torch::Tensor, torch::Tensor> mla_decode(torch::Tensor q_nope, torch:
   p.scale = (float)scale;
   p.lse_base2 = lse_base2 ? 1 : 0;
   p.timeout_ns = env_timeout_ns();
+  p.prof = nullptr;
+  {
+    static const bool prof_on = [] { const char* v = std::getenv("HELIX_A2A_MLA_PROF"); return v && std::string(v) == "1"; }();
+    if (prof_on) {
+      if (!sc.trace.defined()) sc.trace = torch::zeros({helix::kGqaMaxCtas * 4}, q_nope.options().dtype(torch::kInt64));
+      p.prof = reinterpret_cast<unsigned long long*>(sc.trace.data_ptr());
+    }
+  }
   check_cuda(helix::launch_mla_decode(p, env_pdl(), stream), "mla decode launch");
   return std::make_tuple(o, lse);
 }

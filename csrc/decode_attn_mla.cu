@@ -4,9 +4,9 @@
 // All 128 heads share one latent KV stream, so the kernel is bound by tensor-core work, not by HBM.
 // One CTA (8 warps) handles all heads of a sequence for a chunk of its tokens, 32 tokens per tile:
 //   * the fp8 latent rows, their scales and the bf16 rope keys of a tile arrive by bulk async copies
-//     (cp.async.bulk, completion on an mbarrier), two tiles ahead;
-//   * all threads dequantise the tile once into bf16 sub-tiles of [32 tokens x 64 dims] with the
-//     128-byte swizzle.  That single layout serves both products: it is the K-major operand of
+//     (cp.async.bulk, completion on an mbarrier), two tiles ahead, one issuing thread per stream;
+//   * all threads dequantise the tile once (integer bit moves + packed bf16 multiplies, no cvt) into bf16
+//     sub-tiles of [32 tokens x 64 dims] with the 128-byte swizzle.  That single layout serves both products: it is the K-major operand of
 //     S = Q K^T and, read through an MN-major descriptor, the V operand of O = P V (the latent is
 //     both key and value), so nothing is transposed or stored twice;
 //   * S = Q K^T runs on warp-level tensor-core MMAs with the query fragments of the warp's 16 heads
@@ -62,6 +62,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// x holds two e4m3 bytes in the high bytes of its 16-bit halves; returns bf16x2(value * scale).
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2_scaled(uint32_t x, __nv_bfloat162 scale_2p56) {
+  const uint32_t bits = ((x >> 4) & 0x07FF07FFu) | (x & 0x80008000u);
+  const uint32_t k2p64 = 0x5F805F80u;      // bf16x2 (2^64, 2^64)
+  __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&bits);
+  v = __hmul2(v, *reinterpret_cast<const __nv_bfloat162*>(&k2p64));
+  v = __hmul2(v, scale_2p56);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
@@ -110,8 +119,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
   const int head0 = 32 * (warp & 3) + 16 * (warp >> 2);
 
   if (tid == 0) {
-    mbar_init(&full_bar[0], 1);
-    mbar_init(&full_bar[1], 1);
+    mbar_init(&full_bar[0], 3);      // one arrival per issuing thread (latent, scales, rope keys)
+    mbar_init(&full_bar[1], 3);
     mbar_init(&pv_bar[0], 1);
     mbar_init(&pv_bar[1], 1);
     mbar_fence_init();
@@ -148,6 +157,14 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
   const float sl2 = p.scale * kLog2e;
   uint32_t n_full[2] = {0, 0}, n_pv[2] = {0, 0};      // completed phases consumed per barrier
   bool ok = true;
+  const bool prof = p.prof != nullptr && tid == 0;
+  long long pc[7] = {0, 0, 0, 0, 0, 0, 0}, pt = 0;
+#define MLA_PROF(slot)                 \
+  if (prof) {                          \
+    const long long now_c = clock64(); \
+    pc[slot] += now_c - pt;            \
+    pt = now_c;                        \
+  }
 
   while (gcur < g1 && cur_b < p.B && ok) {
     const int b = cur_b;
@@ -185,69 +202,99 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
     }
 
     // producer: bulk copies of one tile (two 16-token units) into staging slot `st`
-    auto issue = [&](int st, int tile) {
-      uint8_t* dst = stage_buf + st * kStageBytes;
-      uint64_t* bar = &full_bar[st];
-      mbar_expect_tx(bar, kStageBytes);
+    // page ids are looked up well ahead of the copies that need them: the (dependent) block-table load
+    // must not sit between a barrier and the Q K^T of the issuing warp
+    auto unit_token = [&](int tile, int u) {
+      // a tile past the end of the block table still copies its full size from the last valid unit
+      return min(tile * kTile + u * kBlk, max(seq_len - 1, 0) / kBlk * kBlk);
+    };
+    auto lookup = [&](int tile, int (&pg)[2]) {
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int tok0 = tile * kTile + u * kBlk;
-        // a tile past the end of the block table still copies its full size from the last valid unit
-        const int tk = min(tok0, max(seq_len - 1, 0) / kBlk * kBlk);
-        const int page = bt[tk / p.page_size];
-        const int64_t row = (int64_t)page * p.page_size + (tk % p.page_size);
-        bulk_g2s(dst + u * (kBlk * kDn), p.ckv + row * kDn, kBlk * kDn, bar);
-        bulk_g2s(dst + kStageLat + u * (kBlk * 16), reinterpret_cast<const uint8_t*>(p.scales) + row * 16, kBlk * 16, bar);
-        bulk_g2s(dst + kStageLat + kStageScl + u * (kBlk * kDr * 2),
-                 reinterpret_cast<const uint8_t*>(p.kpe) + row * kDr * 2, kBlk * kDr * 2, bar);
+      for (int u = 0; u < 2; ++u) pg[u] = bt[unit_token(tile, u) / p.page_size];
+    };
+    // One issuing thread per stream (latent, scales, rope keys): issuing a bulk copy costs its thread on the
+    // order of a hundred cycles, and whoever issues is late for the next barrier; spread over three warps,
+    // none of them warp 0 (which also issues the MMAs), the tile loop no longer waits for one thread.
+    const int stream = (lane == 0 && warp >= 1 && warp <= 3) ? warp - 1 : -1;
+    auto issue = [&](int st, int tile, const int (&pg)[2]) {
+      const uint32_t row_bytes = stream == 0 ? (uint32_t)kDn : stream == 1 ? 16u : (uint32_t)(kDr * 2);
+      const uint8_t* src = stream == 0 ? p.ckv : stream == 1 ? reinterpret_cast<const uint8_t*>(p.scales)
+                                                             : reinterpret_cast<const uint8_t*>(p.kpe);
+      uint8_t* dst = stage_buf + st * kStageBytes + (stream == 0 ? 0 : stream == 1 ? kStageLat : kStageLat + kStageScl);
+      const uint32_t unit_bytes = (uint32_t)kBlk * row_bytes;
+      uint64_t* bar = &full_bar[st];
+      mbar_expect_tx(bar, 2 * unit_bytes);
+      const int tk0 = unit_token(tile, 0), tk1 = unit_token(tile, 1);
+      const int64_t row0 = (int64_t)pg[0] * p.page_size + (tk0 % p.page_size);
+      const int64_t row1 = (int64_t)pg[1] * p.page_size + (tk1 % p.page_size);
+      if (row1 == row0 + kBlk) {                    // both units in one page: one copy
+        bulk_g2s(dst, src + row0 * row_bytes, 2 * unit_bytes, bar);
+      } else {
+        bulk_g2s(dst, src + row0 * row_bytes, unit_bytes, bar);
+        bulk_g2s(dst + unit_bytes, src + row1 * row_bytes, unit_bytes, bar);
       }
     };
-    if (tid == 0) {
-      if (count > 0) issue(0, t_begin);
-      if (count > 1) issue(1, t_begin + 1);
+    if (stream >= 0) {
+      int pg[2];
+      if (count > 0) {
+        lookup(t_begin, pg);
+        issue(0, t_begin, pg);
+      }
+      if (count > 1) {
+        lookup(t_begin + 1, pg);
+        issue(1, t_begin + 1, pg);
+      }
     }
 
     float m_used[2] = {-INFINITY, -INFINITY};   // rows g and g + 8 of this warp's heads
     float l_run[2] = {0.f, 0.f};                 // per-lane partial sums
     bool first_tile = true;
 
+    if (prof) pt = clock64();
+    const long long loop_c0 = pt;
     for (int i = 0; i < count && ok; ++i) {
       const int tile = t_begin + i;
       const int bf = i & 1;                      // kv / P buffer and staging slot
       uint8_t* kv = kv_buf + bf * kKvBytes;
       uint8_t* pb = p_buf + bf * kPBytes;
       const uint8_t* stg = stage_buf + bf * kStageBytes;
+      int pg_next[2] = {0, 0};
+      if (stream >= 0 && i + 2 < count) lookup(tile + 2, pg_next);
       // (a) the P V product that last read these buffers (tile i - 2) must be complete
       if (i >= 2) {
         if (!mbar_wait(&pv_bar[bf], n_pv[bf] & 1, deadline)) ok = false;
         ++n_pv[bf];
       }
-      // (b) this tile's bytes have landed
+      // (b) this tile's bytes have landed.  Every thread waits for itself; a thread whose wait ran out
+      // dequantises garbage into its own chunks and says so at the barrier below.
       if (ok && !mbar_wait(&full_bar[bf], n_full[bf] & 1, deadline)) ok = false;
       ++n_full[bf];
-      if (!__syncthreads_and(ok ? 1 : 0)) {
-        ok = false;
-        break;
-      }
       tc_fence_after_sync();
-      // (c) dequantise: 1024 chunks of 16 fp8 values, four per thread, then the rope keys
+      MLA_PROF(0)
+      // (c) dequantise: 1024 chunks of 16 fp8 values, four per thread, then the rope keys.
+      // No cvt instruction (they issue at a quarter of the ALU rate): an e4m3 byte s.eeee.mmm moved to s.000.0eeee.mmm.0000 IS the bf16 number
+      // 2^-120 times its value, subnormals included, so two packed bf16 multiplies (by 2^64, then by
+      // scale * 2^56; one product could overflow for large scales) finish the job on the FMA pipe.
 #pragma unroll
       for (int r4 = 0; r4 < 4; ++r4) {
+        // Eight consecutive lanes (one phase of a 16-byte shared-memory access) take four chunks of an even
+        // row and the four NEXT-group chunks of the odd row below it: their loads fall in different halves of
+        // the banks, and their swizzled stores in all eight 16-byte bank groups.
         const int idx = tid + r4 * kThreads;     // 0..1023
-        const int row = idx >> 5, c = idx & 31;  // token row, 16-byte chunk of the fp8 row
+        const int q = idx >> 3, j = idx & 7;
+        const int row = 2 * (q >> 3) + (j >> 2);                 // token row
+        const int c = (((q & 7) ^ (j >> 2)) << 2) + (j & 3);     // 16-byte chunk of the fp8 row
         const uint4 raw = *reinterpret_cast<const uint4*>(stg + row * kDn + c * 16);
         const float sc = *reinterpret_cast<const float*>(stg + kStageLat + row * 16 + (c >> 3) * 4);
+        const bool live = tile * kTile + row < seq_len;      // rows past the end must not leak into P V
+        const __nv_bfloat16 s56 = __float2bfloat16_rn(live ? sc * 7.2057594037927936e16f : 0.f);   // 2^56
+        const __nv_bfloat162 sc2 = __halves2bfloat162(s56, s56);
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
         uint32_t out[8];
-        const bool live = tile * kTile + row < seq_len;      // rows past the end must not leak NaNs into P V
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[j] & 0xffffu), __NV_E4M3);
-          const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[j] >> 16), __NV_E4M3);
-          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
-          const float2 bq = __half22float2(*reinterpret_cast<const __half2*>(&hi));
-          out[2 * j] = live ? pack_bf16(a.x * sc, a.y * sc) : 0u;
-          out[2 * j + 1] = live ? pack_bf16(bq.x * sc, bq.y * sc) : 0u;
+          out[2 * j] = e4m3x2_to_bf16x2_scaled(__byte_perm(w[j], 0u, 0x1404), sc2);
+          out[2 * j + 1] = e4m3x2_to_bf16x2_scaled(__byte_perm(w[j], 0u, 0x3424), sc2);
         }
         uint8_t* sub = kv + (c >> 2) * kSubBytes;            // 64-dim sub-tile
         const uint32_t cc = 2u * (c & 3);
@@ -259,11 +306,16 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
         const uint4 v = *reinterpret_cast<const uint4*>(stg + kStageLat + kStageScl + row * 128 + c * 16);
         *reinterpret_cast<uint4*>(kv + 8 * kSubBytes + swz128(row, c)) = v;
       }
-      __syncthreads();
+      if (!__syncthreads_and(ok ? 1 : 0)) {
+        ok = false;
+        break;
+      }
       // the staging slot is free: fetch the tile two ahead
-      if (tid == 0 && i + 2 < count) issue(bf, tile + 2);
+      if (stream >= 0 && i + 2 < count) issue(bf, tile + 2, pg_next);
+      MLA_PROF(1)
 
-      // (d) S = Q K^T for this warp's 16 heads x 32 tokens
+      // (d) S = Q K^T for this warp's 16 heads x 32 tokens.  Bound by the rate of the warp-level MMA pipe
+      // (1152 MMAs per tile in ~2450 cycles); a second set of accumulators changed nothing.
       float s[4][4];
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt)
@@ -286,6 +338,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
           mma_bf16_16816(s[3], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], r2, r3);
         }
       }
+      MLA_PROF(2)
       // (e) online softmax; rows g (values 0, 1 of each n-tile) and g + 8 (values 2, 3)
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -312,7 +365,21 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
           m_used[r] = m_new;
         }
       }
-      // O in tensor memory has to follow the new maxima (rare after the first tiles)
+      // (f) P = exp2(S - m) as the K-major A operand: row = head, 16-byte chunk = n-tile
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const float p0 = fast_exp2(s[nt][0] - m_used[0]), p1 = fast_exp2(s[nt][1] - m_used[0]);
+        const float p2 = fast_exp2(s[nt][2] - m_used[1]), p3 = fast_exp2(s[nt][3] - m_used[1]);
+        l_run[0] += p0 + p1;
+        l_run[1] += p2 + p3;
+        *reinterpret_cast<uint32_t*>(pb + swz128((uint32_t)(head0 + g), (uint32_t)nt) + 4 * t) = pack_bf16(p0, p1);
+        *reinterpret_cast<uint32_t*>(pb + swz128((uint32_t)(head0 + g + 8), (uint32_t)nt) + 4 * t) = pack_bf16(p2, p3);
+      }
+      fence_proxy_async_smem();                  // P and the dequantised tile -> visible to the tensor core
+      tc_fence_before_sync();
+      MLA_PROF(3)
+      // One barrier: P and the dequantised tile are complete, and the warps agree on whether O in tensor
+      // memory has to follow new maxima first (rare after the first tiles).
       if (__syncthreads_or((need && !first_tile) ? 1 : 0)) {
         if (t == 0) {
           s_alpha[head0 + g] = alpha[0];
@@ -342,19 +409,6 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
         __syncthreads();
         tc_fence_after_sync();
       }
-      // (f) P = exp2(S - m) as the K-major A operand: row = head, 16-byte chunk = n-tile
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const float p0 = fast_exp2(s[nt][0] - m_used[0]), p1 = fast_exp2(s[nt][1] - m_used[0]);
-        const float p2 = fast_exp2(s[nt][2] - m_used[1]), p3 = fast_exp2(s[nt][3] - m_used[1]);
-        l_run[0] += p0 + p1;
-        l_run[1] += p2 + p3;
-        *reinterpret_cast<uint32_t*>(pb + swz128((uint32_t)(head0 + g), (uint32_t)nt) + 4 * t) = pack_bf16(p0, p1);
-        *reinterpret_cast<uint32_t*>(pb + swz128((uint32_t)(head0 + g + 8), (uint32_t)nt) + 4 * t) = pack_bf16(p2, p3);
-      }
-      fence_proxy_async_smem();                  // P and the dequantised tile -> visible to the tensor core
-      tc_fence_before_sync();
-      __syncthreads();
       // (g) O += P V on tcgen05: two N = 256 halves, two K = 16 steps each
       if (tid == 0) {
         tc_fence_after_sync();
@@ -370,6 +424,11 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
         umma_commit(&pv_bar[bf]);
       }
       first_tile = false;
+      MLA_PROF(4)
+    }
+    if (prof) {
+      pc[5] += count;
+      pc[6] += clock64() - loop_c0;
     }
 
     // ---- drain: all P V products of this segment ------------------------------------------------
@@ -525,6 +584,9 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
       }
     }
   }
+  if (prof)
+    for (int j = 0; j < 7; ++j) p.prof[(size_t)blockIdx.x * 8 + j] = (unsigned long long)pc[j];
+#undef MLA_PROF
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_o, 512);

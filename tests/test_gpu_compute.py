@@ -119,6 +119,35 @@ def _mla_case(seq_lens, page=16, seed=0):
     return qn, qp, ckv, scales, kpe, bt, torch.tensor(seq_lens, dtype=torch.int32, device="cuda")
 
 
+def test_mla_fp8_dequant_covers_every_e4m3_value(built):
+    """The kernel decodes e4m3 with integer bit moves and bf16 multiplies: check all 254 finite byte values
+    (subnormals, zero, both signs), small and large block scales, through the attention output itself:
+    with one token per sequence the output IS that token's dequantised latent row."""
+    from helix_a2a_b200.ops import attention
+    page = 16
+    finite = [b for b in range(256) if (b & 0x7F) != 0x7F]
+    B = 8
+    codes = torch.tensor(finite, dtype=torch.uint8).repeat(3)[:512]
+    ckv = torch.zeros(B, page, 512, dtype=torch.uint8, device="cuda")
+    scales = torch.ones(B, page, 4, device="cuda")
+    sc_vals = [1.0, 2.0 ** -20, 2.0 ** 20, 3.3e-3, 777.0, 0.37, 2.0 ** 40, 1.5]
+    for b in range(B):
+        ckv[b, 0] = codes.roll(b * 37).cuda()
+        scales[b, 0] = torch.tensor([sc_vals[b], sc_vals[(b + 1) % B], sc_vals[(b + 2) % B], sc_vals[(b + 3) % B]])
+    kpe = torch.zeros(B, page, 64, device="cuda").bfloat16()
+    bt = torch.arange(B, dtype=torch.int32, device="cuda").view(B, 1)
+    sl = torch.ones(B, dtype=torch.int32, device="cuda")
+    qn = torch.zeros(B, 128, 512, device="cuda").bfloat16()
+    qp = torch.zeros(B, 128, 64, device="cuda").bfloat16()
+    o, _ = attention.mla_decode(qn, qp, ckv.view(torch.float8_e4m3fn), scales, kpe, bt, sl, scale=0.1, max_seq_len=1)
+    torch.cuda.synchronize()
+    want = ckv[:, 0].view(torch.float8_e4m3fn).float() * scales[:, 0].repeat_interleave(128, dim=-1)
+    got = o[:, 0].float()                                     # every head sees the same single token
+    tol = want.abs() * 2.0 ** -7 + 1e-30                     # two bf16 roundings (scale, product)
+    assert ((got - want).abs() <= tol).all(), ((got - want).abs() / (want.abs() + 1e-30)).max()
+    assert (o.float() == got[:, None, :]).all()
+
+
 @pytest.mark.parametrize("seq_lens,ctas", [([32], 1), ([100, 7, 64], 1), ([1000, 333], 3), ([4096, 2000, 17, 0], 0),
                                            ([700] * 5, 7)])
 def test_mla_fp8_decode_matches_fp32_reference(built, seq_lens, ctas):
