@@ -149,8 +149,11 @@ def main(argv=None) -> int:
                 t0 = time.time()
                 r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
                 took = time.time() - t0
-                if os.path.isfile(path):
-                    res = json.load(open(path))
+                res = json.load(open(path)) if os.path.isfile(path) else None
+                if res is not None and res.get("completed", 0) == 0:
+                    os.remove(path)          # a point without one completed request is not a result: re-run on resume
+                    print(f"  FAILED: no request completed ({took:.0f}s): {res.get('errors')}", flush=True)
+                elif res is not None:
                     summary.append({"mode": mode, "ctx": ctx, "concurrency": conc,
                                     "tok_per_s": res["output_token_throughput_per_s"],
                                     "itl_ms_mean": res["inter_token_latency_ms"].get("mean"),

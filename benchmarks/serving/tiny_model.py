@@ -33,7 +33,7 @@ def write_tiny_model(out_dir: str, *, layers: int = 4, hidden: int = 1024, heads
         json.dump({"bos_token_id": 1, "eos_token_id": 2, "pad_token_id": 0}, f)
 
     from tokenizers import Tokenizer, models, pre_tokenizers
-    words = ["<pad>", "<s>", "</s>", "<unk>"] + [f"w{i}" for i in range(vocab - 4)]
+    words = ["<pad>", "<s>", "</s>", "<unk>"] + [_word(i) for i in range(vocab - 4)]
     tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
     tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
     # no decoder: transformers joins word-level tokens with single spaces, which round-trips the prompts above
@@ -47,11 +47,17 @@ def write_tiny_model(out_dir: str, *, layers: int = 4, hidden: int = 1024, heads
     return out_dir
 
 
+def _word(i: int) -> str:
+    """Vocabulary word i: at most four characters with its separating space for vocabularies up to 4096
+    (servers bound the prompt's character count by a few characters per token of context before tokenising)."""
+    return format(i, "03x")
+
+
 def synthetic_prompt(n_tokens: int, seed: int = 0, vocab: int = 2048) -> str:
     """A deterministic prompt of exactly ``n_tokens`` word-level tokens (plus BOS if the server adds one)."""
     import random
     rng = random.Random(seed)
-    return " ".join(f"w{rng.randrange(vocab - 4)}" for _ in range(n_tokens))
+    return " ".join(_word(rng.randrange(vocab - 4)) for _ in range(n_tokens))
 
 
 def main(argv=None) -> int:

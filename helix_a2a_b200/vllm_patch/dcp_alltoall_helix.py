@@ -77,6 +77,11 @@ def _init_workspace(cp_rank: int, cp_size: int, cp_group, device: torch.device):
         dist.barrier(cp_group.device_group)
     _workspace, _workspace_key = ws, (cp_size, cp_rank, str(device))
     logger.info("helix workspace ready: rank %d / %d, %s", cp_rank, cp_size, getattr(ws, "_helix_kind", "?"))
+    # one line on stderr as well: inside a serving engine this logger is usually not configured, and an
+    # operator wants to see which exchange a worker really runs
+    import sys
+    print(f"helix_a2a_b200: DCP workspace ready (backend=native, cp_rank={cp_rank}, cp_size={cp_size}, "
+          f"{getattr(ws, '_helix_kind', 'device')} rows, {ws.shape[1] * 8 >> 20} MiB per rank)", file=sys.stderr, flush=True)
     return ws
 
 
