@@ -67,9 +67,10 @@ struct MlaDecodeParams {
   float* part_lse;               // scratch [ctas, 2, 128]
   int* counters;                 // scratch [B], zero on entry and on exit
   int* error_flag;
-  unsigned long long* prof;      // optional [ctas][8] clock64 sums of thread 0: waits, dequantise, Q K^T, softmax (+ rescale),
-                                 // P store + P V issue, tiles, all clocks of the tile loop
+  unsigned long long* prof;      // lockstep kernel only, optional [ctas][8] clock64 sums of thread 0: waits, dequantise,
+                                 // Q K^T, softmax (+ rescale), P store + P V issue, tiles, all clocks of the tile loop
   int B, page_size, ctas;
+  int variant;                   // 0: all warps in lockstep; 1: producer warps + math warps (warp-specialised)
   float scale;
   int lse_base2;
   unsigned long long timeout_ns;

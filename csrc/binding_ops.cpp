@@ -168,6 +168,8 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
 }
 
 
+constexpr int kMlaDefaultVariant = 1;   // warp-specialised
+
 // ---- MLA fp8 paged decode attention -----------------------------------------------------------------
 std::tuple<torch::Tensor, torch::Tensor> mla_decode(torch::Tensor q_nope, torch::Tensor q_pe, torch::Tensor ckv,
                                                     torch::Tensor scales, torch::Tensor kpe, torch::Tensor block_table,
@@ -221,6 +223,11 @@ std::tuple<torch::Tensor, torch::Tensor> mla_decode(torch::Tensor q_nope, torch:
   p.scale = (float)scale;
   p.lse_base2 = lse_base2 ? 1 : 0;
   p.timeout_ns = env_timeout_ns();
+  {
+    // HELIX_A2A_MLA_VARIANT: "ws" = producer warps + math warps, "lockstep" = all warps in lockstep
+    const char* v = std::getenv("HELIX_A2A_MLA_VARIANT");
+    p.variant = (v && std::string(v) == "lockstep") ? 0 : (v && std::string(v) == "ws") ? 1 : kMlaDefaultVariant;
+  }
   p.prof = nullptr;
   {
     static const bool prof_on = [] { const char* v = std::getenv("HELIX_A2A_MLA_PROF"); return v && std::string(v) == "1"; }();

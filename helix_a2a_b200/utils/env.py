@@ -80,3 +80,9 @@ def nccl_impl() -> str:
 def vllm_hook_enabled() -> bool:
     """``HELIX_A2A_VLLM_HOOK=0`` keeps the start-up shim (``vllm_patch/autoload``) from installing the import hook."""
     return os.environ.get("HELIX_A2A_VLLM_HOOK", "1").strip() != "0"
+
+
+def mla_variant() -> str:
+    """``HELIX_A2A_MLA_VARIANT``: ``ws`` (default: producer warps + math warps) or ``lockstep`` (all warps
+    walk the phases of a tile together; the only one with the ``HELIX_A2A_MLA_PROF=1`` cycle profile)."""
+    return os.environ.get("HELIX_A2A_MLA_VARIANT", "ws").strip().lower()

@@ -119,8 +119,10 @@ def _mla_case(seq_lens, page=16, seed=0):
     return qn, qp, ckv, scales, kpe, bt, torch.tensor(seq_lens, dtype=torch.int32, device="cuda")
 
 
-def test_mla_fp8_dequant_covers_every_e4m3_value(built):
-    """The kernel decodes e4m3 with integer bit moves and bf16 multiplies: check all 254 finite byte values
+@pytest.mark.parametrize("variant", ["lockstep", "ws"])
+def test_mla_fp8_dequant_covers_every_e4m3_value(built, monkeypatch, variant):
+    monkeypatch.setenv("HELIX_A2A_MLA_VARIANT", variant)
+    """The kernels decode e4m3 with integer bit moves and bf16 multiplies: check all 254 finite byte values
     (subnormals, zero, both signs), small and large block scales, through the attention output itself:
     with one token per sequence the output IS that token's dequantised latent row."""
     from helix_a2a_b200.ops import attention
@@ -150,8 +152,10 @@ def test_mla_fp8_dequant_covers_every_e4m3_value(built):
 
 @pytest.mark.parametrize("seq_lens,ctas", [([32], 1), ([100, 7, 64], 1), ([1000, 333], 3), ([4096, 2000, 17, 0], 0),
                                            ([700] * 5, 7)])
-def test_mla_fp8_decode_matches_fp32_reference(built, seq_lens, ctas):
+@pytest.mark.parametrize("variant", ["lockstep", "ws"])
+def test_mla_fp8_decode_matches_fp32_reference(built, monkeypatch, seq_lens, ctas, variant):
     import math
+    monkeypatch.setenv("HELIX_A2A_MLA_VARIANT", variant)
     from helix_a2a_b200.ops import attention, reference_math as rm
     from helix_a2a_b200.ops.oproj import check_compute_status
     qn, qp, ckv, scales, kpe, bt, sl = _mla_case(seq_lens, seed=len(seq_lens))
