@@ -111,49 +111,85 @@ class HelixDecodeStack:
         ys = [self.layer(l, q_all[l]) for l in range(self.cfg.n_layers)]
         return torch.stack(ys)
 
-    def _step_last(self, q_all: torch.Tensor) -> torch.Tensor:
+    def _run_layers(self, q_all: torch.Tensor, l0: int, l1: int) -> torch.Tensor:
         y = None
-        for l in range(self.cfg.n_layers):
+        for l in range(l0, l1):
             y = self.layer(l, q_all[l])
         return y
 
+    def _step_last(self, q_all: torch.Tensor) -> torch.Tensor:
+        return self._run_layers(q_all, 0, self.cfg.n_layers)
+
     # ---- end-to-end call: pinned host input -> host output ---------------------------------------
-    def capture(self, q_example: torch.Tensor) -> None:
-        """Capture the whole step in a CUDA graph (call after at least one eager warm-up step)."""
+    def capture(self, q_example: torch.Tensor, head_layers: Optional[int] = None) -> None:
+        """Capture the step in CUDA graphs (call after at least one eager warm-up step).
+
+        Two graphs: the first ``head_layers`` layers and the rest.  ``decode_step_host`` copies the
+        queries of the head layers, starts the head graph, and lets the (much larger) copy of the
+        remaining layers' queries run on a second stream underneath it; the tail graph waits for that
+        copy.  With one graph the whole host-to-device copy sat in front of the first kernel."""
+        L = self.cfg.n_layers
+        if head_layers is None:
+            head_layers = min(8, L // 2)
+        self._head_layers = head_layers if 0 < head_layers < L else 0
         self._static_q = torch.empty_like(q_example, device=self.device)
         self._static_q.copy_(q_example)
+        self._copy_stream = torch.cuda.Stream(device=self.device)
+        self._copy_done = torch.cuda.Event()
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(s):
             self._step_last(self._static_q)
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=s):
-                self._static_y = self._step_last(self._static_q)
+            self._graphs = []
+            bounds = [(0, self._head_layers), (self._head_layers, L)] if self._head_layers else [(0, L)]
+            for l0, l1 in bounds:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=s):
+                    self._static_y = self._run_layers(self._static_q, l0, l1)
+                self._graphs.append(g)
         torch.cuda.current_stream(self.device).wait_stream(s)
-        self._graph = g
+        self._graph = self._graphs[-1]
+
+    def _replay(self) -> None:
+        for g in self._graphs:
+            g.replay()
 
     def decode_step_device(self, q_dev: torch.Tensor) -> torch.Tensor:
         """Step on device-resident ``q``; returns the last layer's ``y`` (``[B, hidden]``)."""
         if self._graph is not None:
             self._static_q.copy_(q_dev, non_blocking=True)
-            self._graph.replay()
+            self._replay()
             return self._static_y
         return self._step_last(q_dev)
 
     def decode_step_host(self, q_pinned: torch.Tensor, out_pinned: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Public end-to-end step: copies ``q`` from pinned host memory, runs every layer, copies
         the result (``[B, hidden]``) back to the host and waits for it."""
-        q_dev = self._static_q if self._graph is not None else torch.empty_like(q_pinned, device=self.device)
-        q_dev.copy_(q_pinned, non_blocking=True)
+        main = torch.cuda.current_stream(self.device)
         if self._graph is not None:
-            self._graph.replay()
+            k = self._head_layers
+            if k:
+                # the previous step ended with a synchronize, so nothing still reads _static_q
+                self._static_q[:k].copy_(q_pinned[:k], non_blocking=True)
+                self._copy_stream.wait_stream(main)
+                with torch.cuda.stream(self._copy_stream):
+                    self._static_q[k:].copy_(q_pinned[k:], non_blocking=True)
+                    self._copy_done.record(self._copy_stream)
+                self._graphs[0].replay()
+                main.wait_event(self._copy_done)
+                self._graphs[1].replay()
+            else:
+                self._static_q.copy_(q_pinned, non_blocking=True)
+                self._replay()
             y = self._static_y
         else:
+            q_dev = torch.empty_like(q_pinned, device=self.device)
+            q_dev.copy_(q_pinned, non_blocking=True)
             y = self._step_last(q_dev)
         if out_pinned is None:
             out_pinned = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
         out_pinned.copy_(y, non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize()
+        main.synchronize()
         return out_pinned
 
     # ---- accounting ------------------------------------------------------------------------------
