@@ -52,8 +52,14 @@ def timeout_ms() -> int:
 
 
 def handle_transport() -> str:
-    """``HELIX_A2A_HANDLE_TRANSPORT``: ``auto`` | ``pidfd`` | ``scm`` | ``cudaipc`` | ``fabric``."""
-    return os.environ.get("HELIX_A2A_HANDLE_TRANSPORT", "auto").strip().lower()
+    """``HELIX_A2A_HANDLE_TRANSPORT``: ``auto`` | ``pidfd`` | ``scm`` | ``fabric`` - how the VMM handles of the
+    workspace rows travel between ranks (POSIX fd duplicated with ``pidfd_getfd``, POSIX fd sent over a Unix
+    socket, or fabric handles).  There is no cudaIpc transport: rows must sit at ``base + rank * stride`` and an
+    IPC mapping lands wherever the driver puts it."""
+    v = os.environ.get("HELIX_A2A_HANDLE_TRANSPORT", "auto").strip().lower()
+    if v not in ("auto", "pidfd", "scm", "fabric"):
+        raise ValueError(f"HELIX_A2A_HANDLE_TRANSPORT={v!r}: expected auto, pidfd, scm or fabric")
+    return v
 
 
 def debug() -> bool:
