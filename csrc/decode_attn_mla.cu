@@ -599,10 +599,12 @@ __global__ void __launch_bounds__(kThreads, 1) mla_decode_kernel(const __grid_co
 // the math.  Warps 0..7 are the math group of the kernel above (Q fragments in registers, Q K^T on warp-level
 // MMAs, softmax, P, one thread issuing P V on tcgen05).  The copies, the dequantisation and the barriers of a
 // tile (about 3000 of its 5500 cycles in the lockstep kernel) now run beside Q K^T instead of in front of it.
-// Registers move from the producers to the math warps with setmaxnreg (168 each at launch -> 40 / 232).
+// Registers move from the producers to the math warps with setmaxnreg (168 each at launch -> 72 / 216; with
+// 40 / 232 the producers spilled and were the slower side, with the rope part of Q in registers the math warps did).
 constexpr int kWsThreads = 384;
 constexpr int kWsStages = 3;
-constexpr int kWsSmem = 2 * kKvBytes + 2 * kPBytes + kWsStages * kStageBytes + 1024;
+constexpr int kQrBytes = kH * 128;   // rope part of Q, [128 heads x 64] bf16, 128-byte swizzle
+constexpr int kWsSmem = 2 * kKvBytes + 2 * kPBytes + kWsStages * kStageBytes + kQrBytes + 1024;
 constexpr int kMathBar = 1, kProdBar = 2;
 constexpr int kProdThreads = 128;
 
@@ -633,6 +635,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) mla_decode_ws_kernel(const __gr
   uint8_t* kv_buf = smem;                                  // 2 x 9 sub-tiles
   uint8_t* p_buf = smem + 2 * kKvBytes;                    // 2 x [128 rows x 128 B]
   uint8_t* stage_buf = p_buf + 2 * kPBytes;                // kWsStages x (latent fp8 | scales | rope)
+  uint8_t* qr_buf = stage_buf + kWsStages * kStageBytes;   // rope part of Q
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
@@ -677,7 +680,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) mla_decode_ws_kernel(const __gr
 
   if (warp >= 8) {
     // =========================== producers ===========================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     const int ptid = tid - 256, pwarp = warp - 8;
     const int stream = (lane == 0 && pwarp < 3) ? pwarp : -1;      // latent, scales, rope keys
     uint32_t n_full[kWsStages] = {0, 0, 0}, fills[2] = {0, 0};
@@ -783,7 +786,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) mla_decode_ws_kernel(const __gr
     if (!ok && ptid == 0) atomicCAS(p.error_flag, 0, (int)kTimeoutMbarrier);
   } else {
     // =========================== math group ===========================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int g = lane >> 2, t = lane & 3;
     const int head0 = 32 * (warp & 3) + 16 * (warp >> 2);
     const float sl2 = p.scale * kLog2e;
@@ -801,28 +804,30 @@ __global__ void __launch_bounds__(kWsThreads, 1) mla_decode_ws_kernel(const __gr
       const bool whole = (t_begin == 0 && t_end == n_tiles);
       const int count = t_end - t_begin;
 
-    // ---- query fragments of this warp's 16 heads: 32 k-steps of the latent part + 4 of the rope part
-    uint32_t qa[36][4];
-    {
-      const __nv_bfloat16* qn = p.q_nope + ((int64_t)b * kH + head0) * kDn;
-      const __nv_bfloat16* qr = p.q_pe + ((int64_t)b * kH + head0) * kDr;
+      // ---- query fragments of this warp's 16 heads: the 32 k-steps of the latent part stay in registers; the
+      // rope part (4 k-steps) sits in shared memory and is re-read with ldmatrix every tile, which keeps the math
+      // warps inside their 232 registers
+      uint32_t qa[32][4];
+      {
+        const __nv_bfloat16* qn = p.q_nope + ((int64_t)b * kH + head0) * kDn;
+        const __nv_bfloat16* qr = p.q_pe + ((int64_t)b * kH + head0) * kDr;
 #pragma unroll
-      for (int ks = 0; ks < 32; ++ks) {
-        qa[ks][0] = *reinterpret_cast<const uint32_t*>(qn + (int64_t)g * kDn + ks * 16 + 2 * t);
-        qa[ks][1] = *reinterpret_cast<const uint32_t*>(qn + (int64_t)(g + 8) * kDn + ks * 16 + 2 * t);
-        qa[ks][2] = *reinterpret_cast<const uint32_t*>(qn + (int64_t)g * kDn + ks * 16 + 8 + 2 * t);
-        qa[ks][3] = *reinterpret_cast<const uint32_t*>(qn + (int64_t)(g + 8) * kDn + ks * 16 + 8 + 2 * t);
-      }
+        for (int ks = 0; ks < 32; ++ks) {
+          qa[ks][0] = *reinterpret_cast<const uint32_t*>(qn + (int64_t)g * kDn + ks * 16 + 2 * t);
+          qa[ks][1] = *reinterpret_cast<const uint32_t*>(qn + (int64_t)(g + 8) * kDn + ks * 16 + 2 * t);
+          qa[ks][2] = *reinterpret_cast<const uint32_t*>(qn + (int64_t)g * kDn + ks * 16 + 8 + 2 * t);
+          qa[ks][3] = *reinterpret_cast<const uint32_t*>(qn + (int64_t)(g + 8) * kDn + ks * 16 + 8 + 2 * t);
+        }
+        __syncwarp();                       // the previous segment's tiles are done with these rows
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        qa[32 + ks][0] = *reinterpret_cast<const uint32_t*>(qr + (int64_t)g * kDr + ks * 16 + 2 * t);
-        qa[32 + ks][1] = *reinterpret_cast<const uint32_t*>(qr + (int64_t)(g + 8) * kDr + ks * 16 + 2 * t);
-        qa[32 + ks][2] = *reinterpret_cast<const uint32_t*>(qr + (int64_t)g * kDr + ks * 16 + 8 + 2 * t);
-        qa[32 + ks][3] = *reinterpret_cast<const uint32_t*>(qr + (int64_t)(g + 8) * kDr + ks * 16 + 8 + 2 * t);
+        for (int r4 = 0; r4 < 4; ++r4) {    // 16 rows x 8 chunks of 16 bytes, four per lane
+          const int idx = lane + 32 * r4, row = idx >> 3, c = idx & 7;
+          const uint4 v = *reinterpret_cast<const uint4*>(qr + (int64_t)row * kDr + c * 8);
+          *reinterpret_cast<uint4*>(qr_buf + swz128((uint32_t)(head0 + row), (uint32_t)c)) = v;
+        }
+        __syncwarp();
       }
-    }
 
-    // producer: bulk copies of one tile (two 16-token units) into staging slot `st`
       float m_used[2] = {-INFINITY, -INFINITY};   // rows g and g + 8 of this warp's heads
       float l_run[2] = {0.f, 0.f};                 // per-lane partial sums
       bool first_tile = true;
@@ -837,8 +842,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) mla_decode_ws_kernel(const __gr
         // the producers have posted this tile
         if (ok && !mbar_wait(&kv_ready[bf], uses[bf] & 1, deadline)) ok = false;
         tc_fence_after_sync();
-      // (d) S = Q K^T for this warp's 16 heads x 32 tokens.  Bound by the rate of the warp-level MMA pipe
-      // (1152 MMAs per tile in ~2450 cycles); a second set of accumulators changed nothing.
+      // (d) S = Q K^T for this warp's 16 heads x 32 tokens, bound by the rate of the warp-level MMA pipe
       float s[4][4];
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt)
@@ -848,17 +852,25 @@ __global__ void __launch_bounds__(kWsThreads, 1) mla_decode_ws_kernel(const __gr
         const int mi = lane >> 3, r8 = lane & 7;
         const uint32_t krow = (uint32_t)(((mi >> 1) << 3) + r8), kcs = (uint32_t)(mi & 1);
         const uint32_t kvb = smem_u32(kv);
+        const uint32_t qrow = (uint32_t)(head0 + ((mi & 1) << 3) + r8), qcs = (uint32_t)(mi >> 1);
+        const uint32_t qrb = smem_u32(qr_buf);
 #pragma unroll
         for (int ks = 0; ks < 36; ++ks) {
           const uint32_t sub = kvb + (uint32_t)(ks >> 2) * kSubBytes;
           const uint32_t cc = 2u * (ks & 3) + kcs;
+          uint32_t a0, a1, a2, a3;
+          if (ks < 32) {
+            a0 = qa[ks < 32 ? ks : 0][0], a1 = qa[ks < 32 ? ks : 0][1], a2 = qa[ks < 32 ? ks : 0][2], a3 = qa[ks < 32 ? ks : 0][3];
+          } else {
+            ldmatrix_x4(qrb + swz128(qrow, 2u * (uint32_t)(ks - 32) + qcs), a0, a1, a2, a3);
+          }
           uint32_t r0, r1, r2, r3;
           ldmatrix_x4(sub + swz128(krow, cc), r0, r1, r2, r3);
-          mma_bf16_16816(s[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], r0, r1);
-          mma_bf16_16816(s[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], r2, r3);
+          mma_bf16_16816(s[0], a0, a1, a2, a3, r0, r1);
+          mma_bf16_16816(s[1], a0, a1, a2, a3, r2, r3);
           ldmatrix_x4(sub + swz128(krow + 16u, cc), r0, r1, r2, r3);
-          mma_bf16_16816(s[2], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], r0, r1);
-          mma_bf16_16816(s[3], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], r2, r3);
+          mma_bf16_16816(s[2], a0, a1, a2, a3, r0, r1);
+          mma_bf16_16816(s[3], a0, a1, a2, a3, r2, r3);
         }
       }
       // (e) online softmax; rows g (values 0, 1 of each n-tile) and g + 8 (values 2, 3)
