@@ -88,7 +88,7 @@ def server_env(helix_backend: str, base=None) -> dict:
     env.setdefault("VLLM_NO_USAGE_STATS", "1")
     env.setdefault("DO_NOT_TRACK", "1")
     # Ranks drift apart by many seconds while vLLM warms up (one rank compiling a kernel the other has cached),
-    # so the device-side waits get a budget that NCCL-like patience needs; a real hang still ends.
+    # so the device-side waits get a limit as patient as a collective library would be; a real hang still ends.
     env.setdefault("HELIX_A2A_TIMEOUT_MS", "120000")
     return env
 

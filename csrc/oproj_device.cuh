@@ -3,7 +3,7 @@
 //
 // `sync_cta()` synchronises the 128 threads that run this body; `wait_input(deadline)` is called by
 // the producer thread after it has requested the first W tiles and before it requests any x tile: it
-// returns once the activations are valid (and false if that never happened within the budget).
+// returns once the activations are valid (and false if that never happened within the time limit).
 #pragma once
 
 #include "helix_common.cuh"

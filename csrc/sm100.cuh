@@ -1,6 +1,6 @@
 // Inline-PTX building blocks for sm_100a: mbarrier, TMA tensor loads, tcgen05 (UMMA) and TMEM.
 //
-// Every wait in here is bounded: the try_wait loops give up after a %globaltimer budget and
+// Every wait in here is bounded: the try_wait loops give up after a %globaltimer time limit and
 // return false, so a kernel that uses them can record an error and exit instead of hanging the
 // GPU.  TMA loads are always issued WITHOUT the cluster-broadcast qualifier: each CTA fetches
 // its own tiles.

@@ -39,7 +39,7 @@ STATUS_NAMES = {
 
 
 class HelixTimeoutError(RuntimeError):
-    """A device-side wait ran out of its budget; the workspace must be reset before reuse."""
+    """A device-side wait ran out of its time limit; the workspace must be reset before reuse."""
 
     def __init__(self, code: int, peer: int, channel: int, entry: int):
         self.code, self.peer, self.channel, self.entry = code, peer, channel, entry

@@ -44,7 +44,7 @@ def backend() -> str:
 
 
 def timeout_ms() -> int:
-    """``HELIX_A2A_TIMEOUT_MS``: budget of every device-side wait (default 2000 ms)."""
+    """``HELIX_A2A_TIMEOUT_MS``: time limit of every device-side wait (default 2000 ms)."""
     try:
         return max(int(os.environ.get("HELIX_A2A_TIMEOUT_MS", "2000")), 1)
     except ValueError:
