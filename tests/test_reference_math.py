@@ -92,3 +92,45 @@ def test_mla_partial_attention_is_attention_over_concat():
     k = torch.cat([ckv, kpe], -1).unsqueeze(1)
     o2, l2 = rm.partial_attention(q, k, ckv.unsqueeze(1), scale)
     assert torch.allclose(o, o2, atol=1e-5) and torch.allclose(l, l2, atol=1e-5)
+
+
+def test_e4m3_bit_move_matches_float8_for_every_code():
+    """The MLA kernels decode e4m3 without a conversion instruction: the byte s.eeee.mmm, moved to
+    s.000.0eeee.mmm.0000, read as bf16, is 2^-120 times its value (subnormals and zero included).
+    Mirror of ``e4m3x2_to_bf16x2_scaled`` in csrc/decode_attn_mla.cu on all 256 codes."""
+    import torch
+    codes = torch.arange(256, dtype=torch.int32)
+    x = codes << 8                                            # the byte in the high byte of a 16-bit half
+    bits = ((x >> 4) & 0x07FF) | (x & 0x8000)
+    as_bf16 = bits.to(torch.int16).view(torch.bfloat16).to(torch.float64)   # exact
+    got = as_bf16 * 2.0 ** 64 * 2.0 ** 56                     # the two multiplies of the kernel (scale 1)
+    want = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).to(torch.float64)
+    finite = ~torch.isnan(want)
+    assert finite.sum() == 254
+    assert torch.equal(got[finite], want[finite])
+    # the first multiply alone stays inside bf16's normal range for every finite code but zero
+    mid = (as_bf16 * 2.0 ** 64)[finite]
+    nz = mid != 0
+    assert (mid[nz].abs() >= 2.0 ** -126).all() and (mid[nz].abs() < 2.0 ** 20).all()
+
+
+def test_streamk_partition_arithmetic():
+    """Mirror of the unit partition of the stream-K o_proj kernel (csrc/oproj_gemm.cu): CTA c owns units
+    [c U / G, (c + 1) U / G); the CTAs that meet a slab are found in closed form, and a slab is written
+    directly only by a CTA that covers all of it."""
+    for slabs, kb_total, G in [(64, 32, 148), (64, 4, 148), (4, 1, 4), (9, 4, 7), (56, 64, 148), (3, 5, 15)]:
+        U = slabs * kb_total
+        if G > U:
+            continue
+        start = [c * U // G for c in range(G + 1)]
+        assert all(start[c + 1] > start[c] for c in range(G))            # every CTA has work
+        for m in range(slabs):
+            t0, t1 = m * kb_total, m * kb_total + kb_total - 1
+            c_first = ((t0 + 1) * G + U - 1) // U - 1
+            c_last = ((t1 + 1) * G + U - 1) // U - 1
+            owners = [c for c in range(G) if start[c] <= t1 and start[c + 1] > t0]
+            assert owners == list(range(c_first, c_last + 1)), (slabs, kb_total, G, m)
+            whole = [c for c in owners if start[c] <= t0 and start[c + 1] > t1]
+            assert (len(owners) == 1) == bool(whole)
+            # piece slots: the CTA that starts the slab uses slot 1, continuations slot 0 - never both for one slab
+            assert start[c_first] <= t0 and all(start[c] > t0 for c in owners[1:])
