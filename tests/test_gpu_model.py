@@ -32,6 +32,17 @@ def test_decode_stack_matches_oracle_and_graph_pdl_replay(native_built):
         pinned = q.cpu().pin_memory()
         host = stack.decode_step_host(pinned)
         assert torch.equal(host.cuda(), eager_last)
+        # the step is two graphs and the later layers' queries are copied under the first one: alternate two
+        # inputs so that a tail graph that started before its copy landed would show the other input's result
+        q2 = torch.randn_like(q)
+        pinned2 = q2.cpu().pin_memory()
+        want = {0: eager_last}
+        for it in range(6):
+            host = stack.decode_step_host(pinned2 if it % 2 else pinned)
+            if it % 2 and 1 not in want:
+                want[1] = host.cuda().clone()
+                assert not torch.equal(want[1], eager_last)
+            assert torch.equal(host.cuda(), want[it % 2])
     finally:
         del os.environ["HELIX_A2A_ENABLE_PDL"]
     check_compute_status(q)
