@@ -92,3 +92,20 @@ def mla_variant() -> str:
     """``HELIX_A2A_MLA_VARIANT``: ``ws`` (default: producer warps + math warps) or ``lockstep`` (all warps
     walk the phases of a tile together; the only one with the ``HELIX_A2A_MLA_PROF=1`` cycle profile)."""
     return os.environ.get("HELIX_A2A_MLA_VARIANT", "ws").strip().lower()
+
+
+def attn_trace() -> bool:
+    """``HELIX_A2A_ATTN_TRACE=1``: the GQA decode attention kernel records four ``%globaltimer`` stamps per
+    CTA (entry, first data, end of streaming, exit; the SM id rides in the low byte of the second)."""
+    return os.environ.get("HELIX_A2A_ATTN_TRACE", "0").strip() == "1"
+
+
+def mla_prof() -> bool:
+    """``HELIX_A2A_MLA_PROF=1``: the lockstep MLA kernel sums ``clock64`` per phase of its tile loop
+    (read back with ``ops().attn_trace``)."""
+    return os.environ.get("HELIX_A2A_MLA_PROF", "0").strip() == "1"
+
+
+def nvtx() -> bool:
+    """``HELIX_A2A_NVTX=1``: NVTX ranges around the Python-level ops (``utils/tracing.py``)."""
+    return os.environ.get("HELIX_A2A_NVTX", "0").strip() == "1"
