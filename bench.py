@@ -214,7 +214,8 @@ def run_helix(args):
                        "global_batch": batch, "seq_len": args.ctx, "parallelism": f"cp{world}",
                        "page_size": cfg.page_size, "kv_tokens_per_gpu_per_seq": local_ctx,
                        "l2": "inputs larger than L2 (KV cache read per step: %.1f GB per GPU)" % (kv_bytes / 1e9),
-                       "cuda_graph": not args.no_graph, "one_kernel_exchange_oproj": world > 1 and args.fuse_oproj, "pdl": os.environ.get("HELIX_A2A_ENABLE_PDL", "0") == "1"},
+                       "cuda_graph": not args.no_graph, "one_kernel_exchange_oproj": world > 1 and args.fuse_oproj, "pdl": os.environ.get("HELIX_A2A_ENABLE_PDL", "0") == "1",
+                       "oproj_weights": "packed once at load time (tile-major, pre-swizzled bf16; same values)" if getattr(stack, "prepack_oproj", False) and not (world > 1 and args.fuse_oproj) else "plain [hidden, K]"},
             "clocks": clocks,
             "e2e": {"value": batch / (ms_e2e * 1e-3), "unit": "tok/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": stack.h2d_bytes_per_step(), "d2h_bytes_per_step": stack.d2h_bytes_per_step()},

@@ -53,6 +53,7 @@ def main():
     ap.add_argument("--only", default="")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--oproj-splits", type=int, default=0, help="0 = pick, -1 = stream-K, n = n K splits")
+    ap.add_argument("--oproj-packed", action="store_true", help="pre-pack the weights (one bulk copy per stage)")
     args = ap.parse_args()
     from helix_a2a_b200.ops import attention
     from helix_a2a_b200.ops.oproj import oproj, check_compute_status
@@ -80,7 +81,11 @@ def main():
             hidden, nl = 8192, max(2, (512 * 1024 * 1024) // (8192 * K * 2))
             ws = [(torch.randn(hidden, K, device="cuda") * 0.02).bfloat16() for _ in range(nl)]
             x = torch.randn(tokens, K, device="cuda").bfloat16()
-            fns = [(lambda l=l: oproj(x, ws[l], splits=args.oproj_splits)) for l in range(nl)]
+            wk = ws
+            if args.oproj_packed:
+                from helix_a2a_b200.ops.oproj import prepack_weight
+                wk = [prepack_weight(w) for w in ws]
+            fns = [(lambda l=l: oproj(x, wk[l], splits=args.oproj_splits)) for l in range(nl)]
             us = time_rotating(fns, args.iters)
             nbytes = hidden * K * 2 + tokens * K * 2 + tokens * hidden * 2
             rows.append({"kernel": "oproj", "tokens": tokens, "K": K, "us": us, "GBs": nbytes / us / 1e3,

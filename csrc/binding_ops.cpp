@@ -301,6 +301,49 @@ torch::Tensor oproj(torch::Tensor x, torch::Tensor w, int64_t splits) {
   return y;
 }
 
+// o_proj on pre-packed weights (see OprojParams::w_packed): `packed` is the uint8 tensor made by
+// helix_a2a_b200.ops.oproj.prepack_weight for a [hidden, K] matrix.  Plain split-K kernel only.
+torch::Tensor oproj_packed(torch::Tensor x, torch::Tensor packed, int64_t hidden64, int64_t K64, int64_t splits) {
+  TORCH_CHECK(x.is_cuda() && packed.is_cuda(), "inputs must be on CUDA");
+  TORCH_CHECK(x.scalar_type() == at::ScalarType::BFloat16 && packed.scalar_type() == at::ScalarType::Byte,
+              "x must be bfloat16, packed uint8");
+  const int hidden = (int)hidden64, K = (int)K64;
+  TORCH_CHECK(x.dim() == 2 && x.size(1) == K && x.stride(1) == 1 && (x.stride(0) * 2) % 16 == 0, "x must be [tokens, K]");
+  TORCH_CHECK(hidden % 128 == 0 && K % 64 == 0, "hidden must be a multiple of 128 and K of 64");
+  TORCH_CHECK(packed.is_contiguous() && (size_t)packed.numel() == helix::oproj_packed_bytes(hidden, K) &&
+                  reinterpret_cast<uintptr_t>(packed.data_ptr()) % 128 == 0,
+              "packed weight has the wrong size or alignment for [", hidden, ", ", K, "]");
+  const int tokens = (int)x.size(0);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  torch::Tensor y = torch::empty({tokens, hidden}, x.options());
+  for (int t0 = 0; t0 < tokens; t0 += 256) {
+    const int nt = std::min(256, tokens - t0);
+    torch::Tensor xs = x.narrow(0, t0, nt);
+    const int n_pad = (nt + 15) / 16 * 16;
+    int sp = (int)splits;
+    if (sp <= 0) sp = helix::oproj_pick_splits(hidden, K, helix::device_sm_count());
+    Scratch& sc = scratch_for(x.device(), hidden / 128 + 1024,
+                              sp > 1 ? (int64_t)helix::oproj_partial_bytes(hidden, sp, n_pad) / 4 : 0, 0);
+    helix::OprojParams p{};
+    p.x_map = mat_map(xs, n_pad);
+    p.w_map = p.x_map;                       // unused with packed weights; keeps the descriptor prefetch valid
+    p.w_packed = packed.data_ptr<uint8_t>();
+    p.packed_atoms = helix::oproj_packed_atoms(K);
+    p.y = reinterpret_cast<__nv_bfloat16*>(y.data_ptr()) + (int64_t)t0 * y.stride(0);
+    p.y_stride = y.stride(0);
+    p.partial = sc.part_a.data_ptr<float>();
+    p.counters = sc.counters.data_ptr<int32_t>() + (sc.counters.numel() - hidden / 128);
+    p.error_flag = sc.error_flag.data_ptr<int32_t>();
+    p.tokens = nt; p.n_pad = n_pad; p.hidden = hidden; p.K = K; p.splits = sp;
+    p.stages = helix::oproj_pick_stages(n_pad);
+    p.atoms = helix::oproj_pick_atoms(n_pad);
+    p.timeout_ns = env_timeout_ns();
+    check_cuda(helix::launch_oproj(p, env_pdl(), stream), "o_proj (packed) launch");
+  }
+  return y;
+}
+
 torch::Tensor attn_trace(torch::Tensor like) {
   Scratch& sc = scratch_for(like.device(), 1, 0, 0);
   TORCH_CHECK(sc.trace.defined(), "no trace recorded: set HELIX_A2A_ATTN_TRACE=1 (or HELIX_A2A_OPROJ_TRACE=1)");
@@ -420,6 +463,7 @@ void register_compute_ops(torch::Library& m) {
       "float scale, bool lse_base2, int ctas, int max_seq_len) -> (Tensor, Tensor)",
       &mla_decode);
   m.def("oproj(Tensor x, Tensor w, int splits) -> Tensor", &oproj);
+  m.def("oproj_packed(Tensor x, Tensor packed, int hidden, int K, int splits) -> Tensor", &oproj_packed);
   m.def(
       "alltoall_combine_oproj(Tensor attn_out, Tensor lse, Tensor w, Tensor workspace, int cp_rank, int cp_size, bool "
       "base2, bool emulate, int timeout_ms) -> (Tensor, Tensor)",

@@ -20,6 +20,11 @@ struct OprojParams {
   int* counters;         // scratch [m_tiles], zero on entry and on exit
   int* error_flag;
   int tokens, n_pad, hidden, K, splits, stages, atoms;   // atoms: 64-wide K atoms per stage (1, 2 or 4)
+  // Optional pre-packed weights (plain kernel only): per 128-row slab, K / 64 atoms (padded to a multiple of 4)
+  // of 16 KB each, every atom already in the 128-byte-swizzled K-major layout the tensor core reads.  A stage
+  // is then ONE contiguous bulk copy instead of `atoms` strided tensor copies.  nullptr: use w_map.
+  const uint8_t* w_packed;
+  int packed_atoms;      // atoms per slab in w_packed (K / 64 rounded up to a multiple of 4)
   int ctas;              // stream-K variant only: CTAs of the launch (splits is ignored there)
   unsigned long long* trace;   // stream-K variant, optional [ctas][8] %globaltimer stamps: entry, set-up done,
                                // first stage landed, last MMA issued, accumulator complete, exit
@@ -35,6 +40,8 @@ int oproj_pick_atoms(int n_pad);
 int oproj_smem_bytes(int n_pad, int stages);
 
 cudaError_t launch_oproj(const OprojParams& p, bool pdl, cudaStream_t stream);
+inline int oproj_packed_atoms(int K) { return ((K + 63) / 64 + 3) / 4 * 4; }
+inline size_t oproj_packed_bytes(int hidden, int K) { return (size_t)(hidden / 128) * oproj_packed_atoms(K) * 16384; }
 
 // Stream-K variant: the (slab, k-block) units are dealt evenly to one CTA per SM, so every SM streams the same
 // share of W whatever hidden / 128 is.  Scratch: partial [ctas][2][n_pad][128] fp32, counters [hidden / 128].

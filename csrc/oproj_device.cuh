@@ -72,6 +72,13 @@ __device__ __forceinline__ void oproj_cta(const OprojParams& p, uint8_t* smem_ra
   if (warp == 0 && lane == 0) {
     // ---------------- producer ----------------
     auto load_w = [&](int s, int i) {
+      if (p.w_packed != nullptr) {
+        // pre-packed weights: the stage's atoms are contiguous and already swizzled
+        bulk_load_1d(smem + (size_t)s * stage_bytes,
+                     p.w_packed + ((size_t)m_tile * p.packed_atoms + (size_t)(kb0 + i) * kAtoms) * atom_a_bytes, a_bytes,
+                     &full_bar[s]);
+        return;
+      }
       for (int a = 0; a < kAtoms; ++a)
         tma_load_2d(smem + (size_t)s * stage_bytes + (size_t)a * atom_a_bytes, &p.w_map, &full_bar[s],
                     (kb0 + i) * kBK + a * kAtomK, m_tile * kBM);

@@ -14,6 +14,7 @@ reference this model runs inside vLLM (``benchmark/sbatch/run_gb200_aiperf_v3.sb
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -62,6 +63,8 @@ class MlaDecodeStack:
         self.scales: List[torch.Tensor] = []
         self.kpe: List[torch.Tensor] = []
         self.w_o: List[torch.Tensor] = []
+        self.prepack_oproj = os.environ.get("HELIX_A2A_OPROJ_PREPACK", "1").strip() != "0"
+        self._w_o_packed = [None] * cfg.n_layers
         for _ in range(cfg.n_layers):
             # quantise in slabs to bound the fp32 temporaries
             ckv = torch.empty(self.n_pages, cfg.page_size, 512, dtype=torch.float8_e4m3fn, device=self.device)
@@ -94,7 +97,17 @@ class MlaDecodeStack:
         if self.cp_size > 1 and self.fuse_oproj:
             return api.alltoall_combine_oproj(o, lse, self.w_o[l], self.workspace, self.cp_rank, self.cp_size)
         x = api.alltoall_combine(o, lse, self.workspace, self.cp_rank, self.cp_size) if self.cp_size > 1 else o
-        return oproj_mod.oproj(x.reshape(self.batch, self.k_local), self.w_o[l])
+        return oproj_mod.oproj(x.reshape(self.batch, self.k_local), self._oproj_weight(l))
+
+    def _oproj_weight(self, l: int):
+        """The layer's o_proj weight in the layout the GEMM streams fastest: packed once, on first use
+        (one contiguous bulk copy per pipeline stage instead of strided tensor copies); the plain matrix
+        stays in ``w_o`` for the one-kernel path and for oracles.  ``prepack_oproj=False`` keeps the plain one."""
+        if not self.prepack_oproj or not self.w_o[l].is_cuda or self.w_o[l].shape[0] % 128 or self.w_o[l].shape[1] % 64:
+            return self.w_o[l]
+        if self._w_o_packed[l] is None:
+            self._w_o_packed[l] = oproj_mod.prepack_weight(self.w_o[l])
+        return self._w_o_packed[l]
 
     def decode_step(self, q_nope_all: torch.Tensor, q_pe_all: torch.Tensor) -> torch.Tensor:
         """``q_nope_all [L, B, 128, 512]``, ``q_pe_all [L, B, 128, 64]`` -> last layer's ``y [B, hidden]``."""

@@ -14,6 +14,7 @@ The reference leaves all of this to vLLM (``benchmark/sbatch/run_gb200_aiperf_v3
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -72,6 +73,8 @@ class HelixDecodeStack:
         self.k_cache: List[torch.Tensor] = []
         self.v_cache: List[torch.Tensor] = []
         self.w_o: List[torch.Tensor] = []
+        self.prepack_oproj = os.environ.get("HELIX_A2A_OPROJ_PREPACK", "1").strip() != "0"
+        self._w_o_packed = [None] * cfg.n_layers
         for _ in range(cfg.n_layers):
             k = torch.empty(shape, dtype=cfg.dtype, device=self.device).normal_(0, kv_std, generator=gen)
             v = torch.empty(shape, dtype=cfg.dtype, device=self.device).normal_(0, kv_std, generator=gen)
@@ -104,7 +107,17 @@ class HelixDecodeStack:
             x = api.alltoall_combine(o, lse, self.workspace, self.cp_rank, self.cp_size)
         else:
             x = o
-        return oproj_mod.oproj(x.reshape(self.batch, self.k_local), self.w_o[l])
+        return oproj_mod.oproj(x.reshape(self.batch, self.k_local), self._oproj_weight(l))
+
+    def _oproj_weight(self, l: int):
+        """The layer's o_proj weight in the layout the GEMM streams fastest: packed once, on first use
+        (one contiguous bulk copy per pipeline stage instead of strided tensor copies); the plain matrix
+        stays in ``w_o`` for the one-kernel path and for oracles.  ``prepack_oproj=False`` keeps the plain one."""
+        if not self.prepack_oproj or not self.w_o[l].is_cuda or self.w_o[l].shape[0] % 128 or self.w_o[l].shape[1] % 64:
+            return self.w_o[l]
+        if self._w_o_packed[l] is None:
+            self._w_o_packed[l] = oproj_mod.prepack_weight(self.w_o[l])
+        return self._w_o_packed[l]
 
     def decode_step(self, q_all: torch.Tensor) -> torch.Tensor:
         """``q_all [L, B, Hq, D]`` on the device -> ``y [L, B, hidden]`` (this rank's partial sums)."""

@@ -109,3 +109,9 @@ def mla_prof() -> bool:
 def nvtx() -> bool:
     """``HELIX_A2A_NVTX=1``: NVTX ranges around the Python-level ops (``utils/tracing.py``)."""
     return os.environ.get("HELIX_A2A_NVTX", "0").strip() == "1"
+
+
+def oproj_prepack() -> bool:
+    """``HELIX_A2A_OPROJ_PREPACK=0``: the model stacks keep the plain ``[hidden, K]`` o_proj weights instead of
+    packing them once into the tile-major, pre-swizzled layout (``ops.oproj.prepack_weight``)."""
+    return os.environ.get("HELIX_A2A_OPROJ_PREPACK", "1").strip() != "0"

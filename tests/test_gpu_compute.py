@@ -93,6 +93,25 @@ def test_oproj_matches_fp32_matmul(built, tokens, hidden, K, splits):
     assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
 
 
+@pytest.mark.parametrize("tokens", [1, 8, 40, 200])
+@pytest.mark.parametrize("hidden,K,splits", [(8192, 1024, 0), (1024, 8192, 0), (512, 320, 1), (1152, 832, 2), (2048, 4096, 4)])
+def test_oproj_prepacked_weight_matches_fp32_matmul(built, tokens, hidden, K, splits):
+    """Pre-packed weights (one bulk copy per stage) give the same product; the source is a column slice."""
+    from helix_a2a_b200.ops.oproj import oproj, prepack_weight, check_compute_status
+    torch.manual_seed(tokens + K)
+    w_full = (torch.randn(hidden, K + 128, device="cuda") * 0.02).bfloat16()
+    w = w_full[:, 64:64 + K]
+    x = torch.randn(tokens, K, device="cuda").bfloat16()
+    pw = prepack_weight(w)
+    y = oproj(x, pw, splits=splits)
+    torch.cuda.synchronize()
+    check_compute_status(x)
+    ref = x.float() @ w.float().t()
+    err = (y.float() - ref).abs().max().item()
+    assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
+    assert torch.equal(y, oproj(x, w, splits=max(splits, 0)) if splits else y)
+
+
 def test_oproj_on_column_slice_of_full_weight(built):
     """Each CP rank multiplies by its K-slice of W_o: a strided view, no copy."""
     from helix_a2a_b200.ops.oproj import oproj

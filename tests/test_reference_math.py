@@ -134,3 +134,26 @@ def test_streamk_partition_arithmetic():
             assert (len(owners) == 1) == bool(whole)
             # piece slots: the CTA that starts the slab uses slot 1, continuations slot 0 - never both for one slab
             assert start[c_first] <= t0 and all(start[c] > t0 for c in owners[1:])
+
+
+def test_oproj_weight_prepack_layout_and_roundtrip():
+    """Packed layout = per slab, per 64-column atom, 128 rows x 128 bytes with chunk c of row r at c ^ (r & 7)."""
+    import torch
+    from helix_a2a_b200.ops.oproj import oproj, packed_atoms, prepack_weight, unpack_weight
+    torch.manual_seed(0)
+    hidden, K = 256, 320                       # 5 atoms -> padded to 8
+    w_full = torch.randn(hidden, 1024).bfloat16()
+    w = w_full[:, 128:128 + K]                 # a column slice, as a CP rank holds it
+    pw = prepack_weight(w)
+    na = packed_atoms(K)
+    assert na == 8 and pw.packed.numel() == (hidden // 128) * na * 16384
+    flat = pw.packed.view(torch.bfloat16)
+    for (row, col) in [(0, 0), (5, 9), (127, 63), (128, 64), (200, 319), (255, 130)]:
+        slab, r, atom, c, e = row // 128, row % 128, col // 64, (col % 64) // 8, col % 8
+        off = ((slab * na + atom) * 128 + r) * 64 + ((c ^ (r & 7)) * 8) + e
+        assert flat[off] == w[row, col], (row, col)
+    # padding atoms are zero, and the inverse gives the matrix back
+    assert (flat.view(hidden // 128, na, 128 * 64)[:, 5:] == 0).all()
+    assert torch.equal(unpack_weight(pw), w.contiguous())
+    x = torch.randn(3, K).bfloat16()
+    assert torch.equal(oproj(x, pw), oproj(x, w.contiguous()))
