@@ -23,12 +23,22 @@ struct GqaDecodeParams {
   const int32_t* seq_lens;     // [B] tokens of the LOCAL KV shard
   __nv_bfloat16* o;            // [B, Hq, 128]
   float* lse;                  // [B, Hq]
-  float* part_o;               // scratch [ctas, 2, 8, 128] fp32: two partial slots per CTA
-  float* part_lse;             // scratch [ctas, 2, 8]
-  int* counters;               // scratch [B * Hkv], zero on entry, zero again on exit
+  float* part_o;               // scratch [2 * ctas + max_helper][8][128] fp32: piece slots
+  float* part_lse;             // scratch [2 * ctas + max_helper][8]
+  // scratch, zero on entry and zero again on exit (gqa_counter_ints(B * Hkv, max_helper) ints):
+  //   [0, P)          blocks of each (sequence, kv head) pair that have been folded into a piece so far
+  //   [P, 2P)         chunks drawn from each pair's dynamic pool          (touched only when dyn_pct > 0)
+  //   [2P]            CTAs that have left the launch                      (touched only when dyn_pct > 0)
+  //   [2P + 8, ...)   one flag per helper slot: a piece has been parked there
+  int* counters;
   int* error_flag;             // set to a helix::Status code when a bounded wait runs out
-  unsigned long long* trace;   // optional [ctas][4] %globaltimer stamps: entry, first data, end of streaming, exit
+  unsigned long long* trace;   // optional [ctas][8] stamps (%globaltimer): entry, first data | SM id, end of the
+                               // static share, exit, end of the last drawn chunk, chunks drawn | pools visited << 32
   int B, Hq, Hkv, page_size, ctas;
+  // Dynamic tail: of every pair with at least dyn_min_blocks KV blocks, the last dyn_pct percent (rounded down to
+  // whole chunks of dyn_chunk blocks) are not part of any CTA's fixed share; CTAs draw them chunk by chunk when
+  // their own share is done, so SMs that stream faster end up streaming more.  dyn_pct = 0: fixed shares only.
+  int dyn_pct, dyn_chunk, dyn_min_blocks, max_helper;
   float scale;
   int lse_base2;
   // 1: the kernel before this one in the stream writes at most the newest token of each sequence (the cache
@@ -39,14 +49,21 @@ struct GqaDecodeParams {
   unsigned long long timeout_ns;
 };
 
-constexpr int kGqaMaxCtas = 640;   // upper bound of the grid (and of the pieces one pair can be cut into)
+constexpr int kGqaMaxCtas = 640;     // upper bound of the grid
+constexpr int kGqaMaxHelper = 1024;  // upper bound of the chunks all dynamic pools hold together
+constexpr int kGqaSeqTable = 256;    // batches beyond this run with fixed shares only
 
-// scratch sizes (independent of the batch: two partial slots per CTA)
-inline size_t gqa_part_o_floats(int ctas) { return (size_t)ctas * 2 * 8 * 128; }
-inline size_t gqa_part_lse_floats(int ctas) { return (size_t)ctas * 2 * 8; }
+// scratch sizes
+constexpr size_t gqa_part_o_floats(int ctas, int max_helper) { return ((size_t)ctas * 2 + max_helper) * 8 * 128; }
+constexpr size_t gqa_part_lse_floats(int ctas, int max_helper) { return ((size_t)ctas * 2 + max_helper) * 8; }
+constexpr size_t gqa_counter_ints(int pairs, int max_helper) { return (size_t)2 * pairs + 8 + max_helper; }
 
 // number of CTAs that fills the device for this batch (two per SM unless the work is tiny)
 int gqa_pick_ctas(int B, int Hkv, int max_seq_len, int sm_count);
+
+// Dynamic-tail settings for a launch of `ctas` CTAs: fills dyn_pct / dyn_chunk / dyn_min_blocks / max_helper of *p
+// (pct_override / chunk_override < 0: the library's choice; max_helper 0 switches the dynamic tail off).
+void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int pct_override, int chunk_override);
 
 cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t stream);
 

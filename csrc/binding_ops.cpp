@@ -28,13 +28,16 @@ bool env_pdl() {
   return v && std::string(v) == "1";
 }
 
-// Per-device scratch owned by the library: error flag, counters, split partials.  Grown on demand,
-// never shrunk; all kernels that use it leave counters at zero.
+// Per-device scratch owned by the library: error flag, counters, split partials.  One set per device (not per
+// stream: calls that may overlap on one GPU must be ordered by the caller).  Grown on demand, never shrunk; a
+// buffer that is outgrown is kept alive until the process ends, because a CUDA graph captured earlier may still
+// hold its address.  All kernels that use the counters leave them at zero.
 struct Scratch {
   torch::Tensor error_flag;    // int32 [1]
   torch::Tensor counters;      // int32 [N]
   torch::Tensor part_a, part_b;  // float32 pools
-  torch::Tensor trace;           // int64 [kGqaMaxCtas * 4], only with HELIX_A2A_ATTN_TRACE=1 / HELIX_A2A_OPROJ_TRACE=1
+  torch::Tensor trace;           // int64 [kGqaMaxCtas * 8], only with HELIX_A2A_ATTN_TRACE=1 / HELIX_A2A_OPROJ_TRACE=1
+  std::vector<torch::Tensor> retired;
 };
 std::mutex g_mu;
 std::map<int, Scratch> g_scratch;
@@ -44,11 +47,22 @@ Scratch& scratch_for(const torch::Device& dev, int64_t counters, int64_t part_a_
   Scratch& s = g_scratch[dev.index()];
   auto iopt = torch::TensorOptions().dtype(torch::kInt32).device(dev);
   auto fopt = torch::TensorOptions().dtype(torch::kFloat32).device(dev);
+  auto grow = [&](torch::Tensor& t, int64_t need, int64_t floor, const torch::TensorOptions& opt, bool zero) {
+    if (t.defined() && t.numel() >= need) return;
+    if (t.defined()) s.retired.push_back(t);
+    const int64_t n = std::max<int64_t>(need + need / 4, floor);     // head-room: regrowing is rare
+    t = zero ? torch::zeros({n}, opt) : torch::empty({n}, opt);
+  };
   if (!s.error_flag.defined()) s.error_flag = torch::zeros({1}, iopt);
-  if (!s.counters.defined() || s.counters.numel() < counters) s.counters = torch::zeros({std::max<int64_t>(counters, 4096)}, iopt);
-  if (!s.part_a.defined() || s.part_a.numel() < part_a_floats) s.part_a = torch::empty({std::max<int64_t>(part_a_floats, 1)}, fopt);
-  if (!s.part_b.defined() || s.part_b.numel() < part_b_floats) s.part_b = torch::empty({std::max<int64_t>(part_b_floats, 1)}, fopt);
+  grow(s.counters, counters, 16384, iopt, true);
+  grow(s.part_a, part_a_floats, 1, fopt, false);
+  grow(s.part_b, part_b_floats, 1, fopt, false);
   return s;
+}
+
+int env_int(const char* name, int dflt) {
+  const char* v = std::getenv(name);
+  return (v && *v) ? std::atoi(v) : dflt;
 }
 
 void check_cuda(cudaError_t e, const char* what) {
@@ -133,8 +147,11 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   torch::Tensor o = torch::empty({B, Hq, 128}, q.options());
   torch::Tensor lse = torch::empty({B, Hq}, q.options().dtype(torch::kFloat32));
   if (B == 0) return std::make_tuple(o, lse);
-  Scratch& sc = scratch_for(q.device(), (int64_t)B * Hkv + 1024, (int64_t)helix::gqa_part_o_floats(sp),
-                            (int64_t)helix::gqa_part_lse_floats(sp));
+  const int max_helper = helix::kGqaMaxHelper;
+  // the o_proj counters sit in the last hidden / 128 ints of the same tensor: leave them room
+  Scratch& sc = scratch_for(q.device(), (int64_t)helix::gqa_counter_ints(B * Hkv, max_helper) + 2048,
+                            (int64_t)helix::gqa_part_o_floats(sp, max_helper),
+                            (int64_t)helix::gqa_part_lse_floats(sp, max_helper));
   helix::GqaDecodeParams p{};
   p.q = reinterpret_cast<const __nv_bfloat16*>(q.data_ptr());
   p.q_stride_b = q.stride(0);
@@ -151,6 +168,11 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   p.counters = sc.counters.data_ptr<int32_t>();
   p.error_flag = sc.error_flag.data_ptr<int32_t>();
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page; p.ctas = sp;
+  // HELIX_A2A_ATTN_DYN_PCT / HELIX_A2A_ATTN_DYN_CHUNK: share of every long pair that is handed out dynamically
+  // (0 = fixed shares only) and the chunk size in 16-token blocks; unset = the library's choice
+  helix::gqa_plan_dynamic(&p, (int)std::max<int64_t>(max_seq_len, 1), max_helper, env_int("HELIX_A2A_ATTN_DYN_PCT", -1),
+                          env_int("HELIX_A2A_ATTN_DYN_CHUNK", -1));
+  if (const int mb = env_int("HELIX_A2A_ATTN_DYN_MIN_BLOCKS", -1); mb >= 0) p.dyn_min_blocks = mb;
   p.scale = (float)scale;
   p.lse_base2 = lse_base2 ? 1 : 0;
   p.timeout_ns = env_timeout_ns();
@@ -158,7 +180,7 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   {
     const char* tr = std::getenv("HELIX_A2A_ATTN_TRACE");
     if (tr && tr[0] == '1') {
-      if (!sc.trace.defined()) sc.trace = torch::zeros({helix::kGqaMaxCtas * 4}, q.options().dtype(torch::kInt64));
+      if (!sc.trace.defined()) sc.trace = torch::zeros({helix::kGqaMaxCtas * 8}, q.options().dtype(torch::kInt64));
       p.trace = reinterpret_cast<unsigned long long*>(sc.trace.data_ptr());
     }
   }
@@ -232,7 +254,7 @@ std::tuple<torch::Tensor, torch::Tensor> mla_decode(torch::Tensor q_nope, torch:
   {
     static const bool prof_on = [] { const char* v = std::getenv("HELIX_A2A_MLA_PROF"); return v && std::string(v) == "1"; }();
     if (prof_on) {
-      if (!sc.trace.defined()) sc.trace = torch::zeros({helix::kGqaMaxCtas * 4}, q_nope.options().dtype(torch::kInt64));
+      if (!sc.trace.defined()) sc.trace = torch::zeros({helix::kGqaMaxCtas * 8}, q_nope.options().dtype(torch::kInt64));
       p.prof = reinterpret_cast<unsigned long long*>(sc.trace.data_ptr());
     }
   }
@@ -291,7 +313,7 @@ torch::Tensor oproj(torch::Tensor x, torch::Tensor w, int64_t splits) {
     if (streamk) {
       static const bool trace_on = [] { const char* v = std::getenv("HELIX_A2A_OPROJ_TRACE"); return v && std::string(v) == "1"; }();
       if (trace_on) {
-        if (!sc.trace.defined()) sc.trace = torch::zeros({helix::kGqaMaxCtas * 4}, x.options().dtype(torch::kInt64));
+        if (!sc.trace.defined()) sc.trace = torch::zeros({helix::kGqaMaxCtas * 8}, x.options().dtype(torch::kInt64));
         p.trace = reinterpret_cast<unsigned long long*>(sc.trace.data_ptr());
       }
     }

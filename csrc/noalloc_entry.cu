@@ -26,6 +26,10 @@ constexpr size_t kPartL = (size_t)HELIX_NOALLOC_MAX_CTAS * 2 * 8 * sizeof(float)
 constexpr size_t kCounters = (size_t)HELIX_NOALLOC_MAX_PAIRS * sizeof(int);
 constexpr size_t kErr = 256;
 constexpr size_t kScratchBytes = kPartO + kPartL + kCounters + kErr;
+static_assert(HELIX_NOALLOC_MAX_CTAS <= helix::kGqaMaxCtas, "the kernel's grid bound sizes the piece slots");
+static_assert(kPartO == helix::gqa_part_o_floats(HELIX_NOALLOC_MAX_CTAS, 0) * sizeof(float) &&
+                  kPartL == helix::gqa_part_lse_floats(HELIX_NOALLOC_MAX_CTAS, 0) * sizeof(float),
+              "scratch layout must match what the kernel indexes");
 
 // The scratch itself.  In host code this name is only a handle for the runtime: its device address
 // is obtained with cudaGetSymbolAddress below and that pointer is what the kernel receives.
@@ -137,6 +141,11 @@ extern "C" __attribute__((visibility("default"))) int helix_gqa_decode_noalloc(
   p.Hkv = kv_heads;
   p.page_size = page_size;
   p.ctas = ctas;
+  // fixed shares only: the dynamic tail of the kernel needs more scratch than this array has
+  p.dyn_pct = 0;
+  p.dyn_chunk = 0;
+  p.dyn_min_blocks = 0;
+  p.max_helper = 0;
   p.scale = scale;
   p.lse_base2 = lse_base2 ? 1 : 0;
   p.timeout_ns = 2000000000ull;
