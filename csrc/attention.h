@@ -29,15 +29,16 @@ struct GqaDecodeParams {
   //   [0, P)          blocks of each (sequence, kv head) pair that have been folded into a piece so far
   //   [P, 2P)         chunks drawn from each pair's dynamic pool          (touched only when dyn_pct > 0)
   //   [2P]            CTAs that have left the launch                      (touched only when dyn_pct > 0)
-  //   [2P + 8, ...)   one flag per helper slot: a piece has been parked there
+  //   [2P + 8, ...)   per helper slot (kGqaMaxVisits per CTA): pair + 1 of the piece parked there
   int* counters;
   int* error_flag;             // set to a helix::Status code when a bounded wait runs out
   unsigned long long* trace;   // optional [ctas][8] stamps (%globaltimer): entry, first data | SM id, end of the
                                // static share, exit, end of the last drawn chunk, chunks drawn | pools visited << 32
   int B, Hq, Hkv, page_size, ctas;
   // Dynamic tail: of every pair with at least dyn_min_blocks KV blocks, the last dyn_pct percent (rounded down to
-  // whole chunks of dyn_chunk blocks) are not part of any CTA's fixed share; CTAs draw them chunk by chunk when
-  // their own share is done, so SMs that stream faster end up streaming more.  dyn_pct = 0: fixed shares only.
+  // whole chunks of dyn_chunk blocks) are not part of any CTA's fixed share; the warps of a CTA whose share is
+  // done draw them chunk by chunk, so SMs that stream faster end up streaming more.  dyn_pct = 0: fixed shares
+  // only.  max_helper: helper piece slots behind the 2 * ctas fixed ones (>= ctas * kGqaMaxVisits, or 0).
   int dyn_pct, dyn_chunk, dyn_min_blocks, max_helper;
   float scale;
   int lse_base2;
@@ -50,7 +51,8 @@ struct GqaDecodeParams {
 };
 
 constexpr int kGqaMaxCtas = 640;     // upper bound of the grid
-constexpr int kGqaMaxHelper = 1024;  // upper bound of the chunks all dynamic pools hold together
+constexpr int kGqaMaxVisits = 4;     // pools of other pairs one CTA may help with (one parked piece each)
+constexpr int kGqaMaxHelper = kGqaMaxCtas * kGqaMaxVisits;   // helper piece slots
 constexpr int kGqaSeqTable = 256;    // batches beyond this run with fixed shares only
 
 // scratch sizes

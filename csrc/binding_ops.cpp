@@ -147,7 +147,9 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   torch::Tensor o = torch::empty({B, Hq, 128}, q.options());
   torch::Tensor lse = torch::empty({B, Hq}, q.options().dtype(torch::kFloat32));
   if (B == 0) return std::make_tuple(o, lse);
-  const int max_helper = helix::kGqaMaxHelper;
+  TORCH_CHECK((int64_t)B * Hkv * ((std::max<int64_t>(max_seq_len, 1) + 15) / 16 + 1) < (int64_t(1) << 31),
+              "B * Hkv * KV blocks must fit 31 bits");
+  const int max_helper = sp * helix::kGqaMaxVisits;
   // the o_proj counters sit in the last hidden / 128 ints of the same tensor: leave them room
   Scratch& sc = scratch_for(q.device(), (int64_t)helix::gqa_counter_ints(B * Hkv, max_helper) + 2048,
                             (int64_t)helix::gqa_part_o_floats(sp, max_helper),

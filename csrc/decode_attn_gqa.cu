@@ -52,7 +52,7 @@ constexpr int kSmemPipe = kWarps * kStages * kStageBytes;   // 98304
 constexpr int kMergeBytes = kWarps * 4 * kD * 4;        // 8192: warps' partial O of four heads / piece list of a fold
 constexpr int kSmemBytes = kSmemPipe + kMergeBytes + 1024;   // + alignment slack
 constexpr int kMaxList = kMergeBytes / 4;               // pieces one fold can list
-static_assert(kGqaMaxCtas + kGqaMaxHelper <= kMaxList, "a fold lists at most one piece per CTA plus every helper slot");
+static_assert(2 * kGqaMaxCtas <= kMaxList, "a fold lists at most one fixed piece and one helper piece per CTA");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -188,11 +188,9 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
   __shared__ __align__(8) uint64_t full_bar[kWarps][kStages];
   __shared__ float s_m[kWarps][8], s_l[kWarps][8];
   __shared__ int s_flag;                         // CTA-wide broadcast word (last arrival, scan result, list length)
-  __shared__ int s_draw[2];                      // chunk drawn ahead by thread 0 (two slots, used alternately)
-  __shared__ int s_scan;                         // chunk drawn while probing the other pools
+  __shared__ int s_dynblk[2];                    // pool blocks the warps streamed in this segment (two slots, alternating)
   __shared__ int s_nb[kGqaSeqTable];             // KV blocks of each sequence
   __shared__ unsigned short s_nc[kGqaSeqTable];  // chunks in each of its pairs' pools
-  __shared__ int s_hb[kGqaSeqTable];             // first helper slot of the sequence's pools
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -207,13 +205,15 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
     mbar_fence_init();
     tma_prefetch_desc(&p.k_map);
     tma_prefetch_desc(&p.v_map);
+    s_dynblk[0] = 0;
+    s_dynblk[1] = 0;
   }
   const bool early_kv = p.kv_stable != 0;
   if (!early_kv) asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const unsigned long long t_entry = now_ns();
   const unsigned long long deadline = t_entry + p.timeout_ns;
-  unsigned long long t_first = 0, t_static = 0, t_dyn = 0;
+  unsigned long long t_static = 0, t_dyn = 0;
   unsigned n_drawn = 0, n_visits = 0;
 
   // ---- per-sequence tables and totals ------------------------------------------------------------
@@ -222,26 +222,21 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
   const int n_tab = min(p.B, kGqaSeqTable);
   for (int i = tid; i < n_tab; i += kThreads) s_nb[i] = blocks_of(p.seq_lens[i]);
   __syncthreads();
-  long long total_s = 0;                         // blocks in the fixed shares
+  int total_s = 0;                               // blocks in the fixed shares (the host checked that this fits an int)
   {
     long long total = 0;
     for (int b = 0; b < n_tab; ++b) total += s_nb[b];
     for (int b = kGqaSeqTable; b < p.B; ++b) total += blocks_of(p.seq_lens[b]);
-    // A pair only gets a pool if what stays in the fixed shares is longer than any share: a CTA's share then
+    // A pair only gets a pool if what stays in the fixed shares is longer than any share.  A CTA's share then
     // never holds such a pair from its first block to its last fixed block, so the share's two piece slots
-    // (one for a pair it continues, one for a pair it starts) still suffice.
+    // (one for a pair it continues, one for a pair it starts) still suffice; and some share ends inside the
+    // pair, so the pair has at least one CTA that stays on its pool until the pool is empty.
     const long long share_max = (total * Hkv + G - 1) / G;
-    int hb = 0;
     for (int b = 0; b < n_tab; ++b) {
       const int nb = s_nb[b];
       int nc = dyn_on ? dyn_chunks_of(nb, p.dyn_pct, cd, p.dyn_min_blocks) : 0;
-      if (nb - nc * cd <= share_max) nc = 0;
-      if (hb + nc * Hkv > p.max_helper || nc > 65535) nc = 0;    // never more chunks than helper slots
-      if (tid == 0) {
-        s_nc[b] = (unsigned short)nc;
-        s_hb[b] = hb;
-      }
-      hb += nc * Hkv;
+      if (nb - nc * cd <= share_max || nc > 65535) nc = 0;
+      if (tid == 0) s_nc[b] = (unsigned short)nc;
       total_s += nb - nc * cd;
     }
     for (int b = kGqaSeqTable; b < p.B; ++b) total_s += blocks_of(p.seq_lens[b]);
@@ -252,42 +247,45 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
   auto seq_nc = [&](int b) { return (dyn_on && b < kGqaSeqTable) ? (int)s_nc[b] : 0; };
   auto seq_ns = [&](int b) { return seq_nb(b) - seq_nc(b) * cd; };
 
-  const long long share = max((total_s + G - 1) / (long long)G, 1LL);
-  const long long g0 = (long long)blockIdx.x * share;
-  const long long g1 = min(total_s, g0 + share);
+  const int share = max((total_s + G - 1) / G, 1);
+  const int g0 = (int)min((long long)blockIdx.x * share, (long long)total_s);
+  const int g1 = min(total_s, g0 + share);
 
-  int* const done_ctr = p.counters;                      // [P]
-  int* const pool_ctr = p.counters + (size_t)p.B * Hkv;   // [P]
-  int* const exit_ctr = p.counters + (size_t)2 * p.B * Hkv;
-  int* const helper_flag = exit_ctr + 8;                 // [max_helper]
   const int P = p.B * Hkv;
+  int* const done_ctr = p.counters;              // [P]
+  int* const pool_ctr = p.counters + P;          // [P]
+  int* const exit_ctr = p.counters + 2 * P;
+  int* const helper_pair = exit_ctr + 8;         // [max_helper]: pair + 1 of the piece parked in each helper slot
 
   uint8_t* my_smem = smem + warp * (kStages * kStageBytes);
   const float sl2 = p.scale * kLog2e;
   const int mi = lane >> 3, r8 = lane & 7;
   const uint32_t k_row = (uint32_t)(((mi >> 1) << 3) + r8), k_csel = (uint32_t)(mi & 1);
   const uint32_t v_row = (uint32_t)(((mi & 1) << 3) + r8), v_csel = (uint32_t)(mi >> 1);
-  int it_ring = 0;           // TMA iterations issued so far by this warp: fixes stage and parity
+  int it_ring = 0;           // TMA iterations consumed so far by this warp: fixes stage and parity
   bool ok = true;
 
-  // ---- segments: a run of blocks of one pair that this CTA streams in one go -----------------------
+  // ---- segments: blocks of one pair that this CTA streams in one go ---------------------------------
+  // [kb_begin, kb_end) are blocks of the fixed share (warp w takes kb_begin + w, + W, ...); with `pool` the warps
+  // then go on drawing chunks of cd blocks from the pair's pool until it is empty.
   struct Seg {
     int b, kvh, kb_begin, kb_end, n_blocks, seq_len;
     int slot;                // piece slot, should this segment open a new running state
-    bool valid;
+    bool pool, valid;
   };
   int cur_b = 0;
-  long long base = 0;        // share-space index of block 0 of (cur_b, kvh = 0)
+  int base = 0;              // share-space index of block 0 of (cur_b, kvh = 0)
   while (cur_b < p.B) {
-    const long long span = (long long)seq_ns(cur_b) * Hkv;
+    const int span = seq_ns(cur_b) * Hkv;
     if (g0 < base + span) break;
     base += span;
     ++cur_b;
   }
-  long long gcur = g0;
+  int gcur = g0;
   auto next_static = [&]() {
     Seg sg;
     sg.valid = false;
+    sg.pool = false;
     while (gcur < g1 && cur_b < p.B) {
       const int ns = seq_ns(cur_b);
       if (ns == 0) {
@@ -297,95 +295,144 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
       sg.b = cur_b;
       sg.seq_len = p.seq_lens[cur_b];
       sg.n_blocks = seq_nb(cur_b);
-      sg.kvh = (int)((gcur - base) / ns);
-      sg.kb_begin = (int)((gcur - base) - (long long)sg.kvh * ns);
-      sg.kb_end = (int)min((long long)ns, (long long)sg.kb_begin + (g1 - gcur));
+      sg.kvh = (gcur - base) / ns;
+      sg.kb_begin = (gcur - base) - sg.kvh * ns;
+      sg.kb_end = min(ns, sg.kb_begin + (g1 - gcur));
       sg.slot = blockIdx.x * 2 + (sg.kb_begin == 0 ? 1 : 0);   // slot 1: the piece that starts its pair
       sg.valid = true;
       gcur += (sg.kb_end - sg.kb_begin);
+      sg.pool = gcur >= g1 && seq_nc(cur_b) > 0;    // the share ends here: carry on with this pair's pool
       if (sg.kvh == Hkv - 1 && sg.kb_end == ns) {   // the next segment starts the next sequence
-        base += (long long)ns * Hkv;
+        base += ns * Hkv;
         ++cur_b;
       }
       break;
     }
     return sg;
   };
-  auto chunk_seg = [&](int b, int kvh, int c) {
+  int n_pieces_parked = 0;   // helper slots this CTA has used
+  auto pool_seg = [&](int pair) {
     Seg sg;
-    const int nc = seq_nc(b);
-    sg.b = b;
-    sg.kvh = kvh;
-    sg.n_blocks = seq_nb(b);
-    sg.seq_len = p.seq_lens[b];
-    sg.kb_begin = sg.n_blocks - (nc - c) * cd;
-    sg.kb_end = sg.kb_begin + cd;
-    sg.slot = 2 * G + s_hb[b] + kvh * nc + c;
+    sg.b = pair / Hkv;
+    sg.kvh = pair % Hkv;
+    sg.n_blocks = seq_nb(sg.b);
+    sg.seq_len = p.seq_lens[sg.b];
+    sg.kb_begin = sg.kb_end = 0;
+    sg.slot = 2 * G + blockIdx.x * kGqaMaxVisits + n_pieces_parked;
+    sg.pool = true;
     sg.valid = true;
     return sg;
   };
-  // Find a pool that still has chunks, starting at pair `start`, and draw one.  Uniform over the CTA.
-  auto scan_pools = [&](int start) {
-    Seg sg;
-    sg.valid = false;
-    int off = 0;
-    while (off < P) {
-      bool avail = false;
-      if (off + tid < P) {
-        const int q = (int)(((long long)start + off + tid) % P);
-        const int nc = seq_nc(q / Hkv);
-        if (nc > 0) avail = ld_relaxed(pool_ctr + q) < nc;
-      }
+  // probe of the pools after `start` (one per thread); stale answers are fine: a pool never refills
+  auto probe = [&](int start, int off, int exclude) {
+    bool avail = false;
+    if (off + tid < P) {
+      const int q = (int)(((long long)start + off + tid) % P);
+      const int nc = seq_nc(q / Hkv);
+      if (nc > 0 && q != exclude) avail = ld_relaxed(pool_ctr + q) < nc;
+    }
+    return avail;
+  };
+  // Pick a pool that (probably) still has chunks, starting at pair `start`.  Uniform over the CTA.
+  auto pick_pool = [&](int start, bool have_pre, bool pre) {
+    for (int off = 0; off < P; off += kThreads) {
+      const bool avail = (off == 0 && have_pre) ? pre : probe(start, off, -1);
       if (tid == 0) s_flag = INT_MAX;
       __syncthreads();
       if (avail) atomicMin(&s_flag, off + tid);
       __syncthreads();
       const int f = s_flag;
-      if (f == INT_MAX) {
-        off += kThreads;
-        __syncthreads();
-        continue;
-      }
-      const int q = (int)(((long long)start + f) % P);
-      if (tid == 0) s_scan = atomicAdd(pool_ctr + q, 1);
       __syncthreads();
-      const int c = s_scan;
-      __syncthreads();
-      if (c < seq_nc(q / Hkv)) {
-        ++n_visits;
-        ++n_drawn;
-        return chunk_seg(q / Hkv, q % Hkv, c);
-      }
-      // somebody else took the pool's last chunk in between: it shows as empty on the next probe
+      if (f != INT_MAX) return (int)(((long long)start + f) % P);
     }
-    return sg;
+    return -1;
   };
 
-  auto issue = [&](const Seg& sg, int ring, int kb, int page) {
-    const int tip = (kb * kBlockTok) % p.page_size;
-    uint8_t* dst = my_smem + (ring % kStages) * kStageBytes;
-    uint64_t* bar = &full_bar[warp][ring % kStages];
-    mbar_expect_tx(bar, kStageBytes);
-    tma_load_4d(dst, &p.k_map, bar, 0, tip, sg.kvh, page);
-    tma_load_4d(dst + 2048, &p.k_map, bar, 64, tip, sg.kvh, page);
-    tma_load_4d(dst + kTileBytes, &p.v_map, bar, 0, tip, sg.kvh, page);
-    tma_load_4d(dst + kTileBytes + 2048, &p.v_map, bar, 64, tip, sg.kvh, page);
-  };
-  // first loads of a segment; called while the previous segment is still being merged, so the
-  // ramp of one segment hides behind the epilogue of the one before
-  auto prologue = [&](const Seg& sg) {
-    const int32_t* bt = p.block_table + (int64_t)sg.b * p.bt_stride;
-    const int my_first = sg.kb_begin + warp;
-    const int my_count = my_first < sg.kb_end ? (sg.kb_end - my_first + kWarps - 1) / kWarps : 0;
-    int pg[kStages];
-#pragma unroll
-    for (int i = 0; i < kStages; ++i)
-      pg[i] = i < my_count ? bt[((my_first + i * kWarps) * kBlockTok) / p.page_size] : 0;
-    if (lane == 0) {
-#pragma unroll
-      for (int i = 0; i < kStages; ++i)
-        if (i < my_count) issue(sg, it_ring + i, my_first + i * kWarps, pg[i]);
+  // ---- per-warp loader: which block comes next, and the loads in flight -------------------------------
+  int ld_mode = 2;           // 0: blocks of the fixed share, 1: chunks drawn from the pool, 2: nothing more
+  int ld_kb = 0, ld_end = 0, ld_kvh = 0, ld_nc = 0, ld_ns = 0;
+  bool ld_pool = false;
+  const int32_t* ld_bt = p.block_table;
+  int* ld_ctr = pool_ctr;
+  int ck_kb = 0, ck_left = 0, c_raw = 0;         // current chunk; the draw in flight lives in lane 0's c_raw
+  int pend_kb = 0, pend_page = 0;
+  bool pend_valid = false;
+  int issued = 0, consumed = 0, my_dyn = 0;
+  int kq0 = 0, kq1 = 0, kq2 = 0;                 // block index of the load in each ring stage
+
+  auto gen_advance = [&]() {
+    pend_valid = false;
+    if (ld_mode == 0) {
+      if (ld_kb < ld_end) {
+        pend_kb = ld_kb;
+        ld_kb += kWarps;
+        pend_valid = true;
+      } else {
+        ld_mode = ld_pool ? 1 : 2;
+        if (p.trace != nullptr && ld_pool && t_static == 0) t_static = now_ns();
+      }
     }
+    if (!pend_valid && ld_mode == 1) {
+      if (ck_left == 0) {
+        const int c = __shfl_sync(0xffffffffu, c_raw, 0);
+        if (c < ld_nc) {
+          ck_kb = ld_ns + c * cd;
+          ck_left = cd;
+          ++n_drawn;
+          if (lane == 0) c_raw = atomicAdd(ld_ctr, 1);   // the next draw: its round trip hides behind this chunk
+        } else {
+          ld_mode = 2;
+        }
+      }
+      if (ld_mode == 1) {
+        pend_kb = ck_kb++;
+        --ck_left;
+        ++my_dyn;
+        pend_valid = true;
+      }
+    }
+    // the page id is looked up one block ahead of the copy that needs it, so the (dependent) block-table
+    // load never stalls the warp in front of a copy
+    if (pend_valid) pend_page = ld_bt[(pend_kb * kBlockTok) / p.page_size];
+  };
+  auto issue_pending = [&]() {
+    const int ring = it_ring + issued;
+    const int stage = ring % kStages;
+    if (lane == 0) {
+      const int tip = (pend_kb * kBlockTok) % p.page_size;
+      uint8_t* dst = my_smem + stage * kStageBytes;
+      uint64_t* bar = &full_bar[warp][stage];
+      mbar_expect_tx(bar, kStageBytes);
+      tma_load_4d(dst, &p.k_map, bar, 0, tip, ld_kvh, pend_page);
+      tma_load_4d(dst + 2048, &p.k_map, bar, 64, tip, ld_kvh, pend_page);
+      tma_load_4d(dst + kTileBytes, &p.v_map, bar, 0, tip, ld_kvh, pend_page);
+      tma_load_4d(dst + kTileBytes + 2048, &p.v_map, bar, 64, tip, ld_kvh, pend_page);
+    }
+    if (stage == 0) kq0 = pend_kb;
+    else if (stage == 1) kq1 = pend_kb;
+    else kq2 = pend_kb;
+    ++issued;
+    gen_advance();
+  };
+  // Point the loader at a segment and request its first blocks.  Called while the previous segment is still
+  // being merged, so the ramp of one segment hides behind the epilogue of the one before.
+  auto seg_begin = [&](const Seg& sg) {
+    ld_mode = 0;
+    ld_kb = sg.kb_begin + warp;
+    ld_end = sg.kb_end;
+    ld_kvh = sg.kvh;
+    ld_pool = sg.pool;
+    ld_nc = seq_nc(sg.b);
+    ld_ns = sg.n_blocks - ld_nc * cd;
+    ld_bt = p.block_table + (int64_t)sg.b * p.bt_stride;
+    ld_ctr = pool_ctr + (sg.b * Hkv + sg.kvh);
+    ck_left = 0;
+    issued = consumed = 0;
+    my_dyn = 0;
+    c_raw = INT_MAX;
+    if (ld_pool && lane == 0) c_raw = atomicAdd(ld_ctr, 1);
+    gen_advance();
+    while (issued < kStages && pend_valid) issue_pending();
   };
 
   float* s_o = reinterpret_cast<float*>(smem + kSmemPipe);   // [kWarps][4][kD]: merge buffer, not part of the rings
@@ -394,18 +441,23 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
   Seg cur = next_static();
   if (early_kv) {
     // old KV does not depend on the kernel before us: request the first tiles, then wait for it (q does depend).
-    // A segment that reaches the newest token waits first: that token's K/V row may still be on its way.
-    const bool touches_newest = cur.valid && cur.kb_end == cur.n_blocks;
-    if (touches_newest) asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (cur.valid) prologue(cur);
-    if (!touches_newest) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // A segment that reaches the newest token, or that draws from a pool (the counters are re-armed by the
+    // launch before this one), waits first.
+    const bool wait_first = cur.valid && (cur.kb_end == cur.n_blocks || cur.pool);
+    if (wait_first) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (cur.valid) seg_begin(cur);
+    if (!wait_first) asm volatile("griddepcontrol.wait;" ::: "memory");
   } else if (cur.valid) {
-    prologue(cur);
+    seg_begin(cur);
   }
-  bool in_static = cur.valid;
+  int n_attempts = 0;
   if (!cur.valid && dyn_on) {          // no fixed share (more CTAs than blocks): go straight to the pools
-    cur = scan_pools(blockIdx.x % max(P, 1));
-    if (cur.valid) prologue(cur);
+    const int q = pick_pool(blockIdx.x % max(P, 1), false, false);
+    ++n_attempts;
+    if (q >= 0) {
+      cur = pool_seg(q);
+      seg_begin(cur);
+    }
   }
 
   // ---- running state of the pair this CTA is accumulating ------------------------------------------
@@ -422,7 +474,6 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
 
   while (cur.valid) {
     const int b = cur.b, kvh = cur.kvh, seq_len = cur.seq_len;
-    const int kb_begin = cur.kb_begin, kb_end = cur.kb_end;
     if (!st_active) {
       st_active = true;
       st_b = b;
@@ -442,31 +493,17 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
         }
       }
     }
-    // What follows this segment?  More of the fixed share, or (when that is done) a chunk of this pair's
-    // pool, drawn now so that the atomic's round trip hides behind the streaming below.
-    const bool static_more = in_static && gcur < g1;
-    const int my_nc = seq_nc(b);
-    const bool drew = !static_more && dyn_on && my_nc > 0;
-    dpar ^= 1;
-    if (drew && tid == 0) s_draw[dpar] = atomicAdd(pool_ctr + (b * Hkv + kvh), 1);
+    // a look at the other pools now tells, when this segment is done, where to go next without a round trip
+    const bool pre = cur.pool ? probe(b * Hkv + kvh + 1, 0, b * Hkv + kvh) : false;
 
-    const int32_t* bt = p.block_table + (int64_t)b * p.bt_stride;
-    // page ids are looked up one iteration ahead of the TMA that needs them, so the (dependent)
-    // block-table load never stalls the warp in front of a copy
-    auto page_of = [&](int kb) { return bt[(kb * kBlockTok) / p.page_size]; };
-    const int my_first = kb_begin + warp;
-    const int my_count = my_first < kb_end ? (kb_end - my_first + kWarps - 1) / kWarps : 0;
-    int next_page = kStages < my_count ? page_of(my_first + kStages * kWarps) : 0;
-
-    for (int it = 0; it < my_count; ++it) {
-      const int ring = it_ring + it;
+    while (consumed < issued) {
+      const int ring = it_ring + consumed;
       const int stage = ring % kStages;
-      const int kb = my_first + it * kWarps;
       if (!mbar_wait(&full_bar[warp][stage], (uint32_t)((ring / kStages) & 1), deadline)) {
         ok = false;
         break;
       }
-      if (p.trace != nullptr && t_first == 0) t_first = now_ns();
+      const int kb = stage == 0 ? kq0 : (stage == 1 ? kq1 : kq2);
       const uint32_t kbase = smem_u32(my_smem + stage * kStageBytes);
       const uint32_t vbase = kbase + kTileBytes;
 
@@ -529,45 +566,43 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
         mma_bf16_16816(o_acc[2 * jj], pa0, 0u, pa2, 0u, r0, r1);
         mma_bf16_16816(o_acc[2 * jj + 1], pa0, 0u, pa2, 0u, r2, r3);
       }
-      // this stage is free again: fetch the block kStages iterations ahead
+      ++consumed;
+      // this stage is free again: fetch the block kStages ahead
       __syncwarp();
-      if (lane == 0 && it + kStages < my_count) issue(cur, ring + kStages, kb + kStages * kWarps, next_page);
-      if (it + 1 + kStages < my_count) next_page = page_of(kb + (kStages + 1) * kWarps);
+      if (pend_valid) issue_pending();
     }
-    it_ring += my_count;
-    st_blocks += kb_end - kb_begin;
+    it_ring += consumed;
+    dpar ^= 1;
+    if (lane == 0 && my_dyn != 0) atomicAdd(&s_dynblk[dpar], my_dyn);
     // The vote makes a timeout of one warp a decision of the whole CTA, so no warp is ever left
     // alone at a barrier; it also orders the next merge after the reads of the previous one and
-    // publishes thread 0's drawn chunk.
+    // publishes the warps' pool block counts.
     if (!__syncthreads_and(ok ? 1 : 0)) {
       ok = false;
       break;
     }
-    if (p.trace != nullptr) {
-      if (in_static) t_static = now_ns();
-      else t_dyn = now_ns();
-    }
+    if (p.trace != nullptr) t_dyn = now_ns();
+    st_blocks += (cur.kb_end - cur.kb_begin) + s_dynblk[dpar];
     // ---- pick the next segment and start streaming it before the epilogue of this one ---------------
-    Seg nxt;
-    nxt.valid = false;
-    if (static_more) nxt = next_static();
-    if (!nxt.valid) {
-      in_static = false;
-      if (dyn_on) {
-        const int c = drew ? s_draw[dpar] : INT_MAX;
-        if (c < my_nc) {
-          nxt = chunk_seg(b, kvh, c);
-          ++n_drawn;
-        } else {
-          nxt = scan_pools(b * Hkv + kvh + 1);
-        }
-      }
+    Seg nxt = next_static();
+    if (!nxt.valid && dyn_on && n_pieces_parked < kGqaMaxVisits && n_attempts < 2 * kGqaMaxVisits) {
+      const int q = pick_pool(b * Hkv + kvh + 1, cur.pool, pre);
+      ++n_attempts;
+      if (q >= 0) nxt = pool_seg(q);
     }
-    if (nxt.valid) prologue(nxt);
+    if (nxt.valid) seg_begin(nxt);
+    if (tid == 0) s_dynblk[dpar] = 0;     // the next use of this slot is two barriers away
 
-    if (!nxt.valid || nxt.b != st_b || nxt.kvh != st_kvh) {
+    const bool leave = !nxt.valid || nxt.b != st_b || nxt.kvh != st_kvh;
+    if (leave && st_blocks == 0) st_active = false;      // a pool that turned out to be empty: nothing to park
+    if (leave && st_blocks != 0) {
       // ---- leave the pair: merge the warps' partials, four heads per round --------------------------
       const bool whole = (st_blocks == st_nb);
+      const bool helper = st_slot >= 2 * G;
+      if (helper) {
+        ++n_pieces_parked;
+        ++n_visits;
+      }
       float* part_o = p.part_o + (size_t)st_slot * 8 * kD;
       float* part_l = p.part_lse + (size_t)st_slot * 8;
       float l_quad = l_run;
@@ -624,7 +659,7 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
         const int pair = st_b * Hkv + st_kvh;
         __syncthreads();
         if (tid == 0) {
-          if (st_slot >= 2 * G) helper_flag[st_slot - 2 * G] = 1;
+          if (helper) helper_pair[st_slot - 2 * G] = pair + 1;
           const int prev = atom_add_acq_rel(done_ctr + pair, st_blocks);
           s_flag = (prev + st_blocks == st_nb);
         }
@@ -633,26 +668,28 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
         if (completes) {
           // ---- this piece completed the pair: fold all of its pieces ---------------------------------
           __syncthreads();                    // everybody has read the verdict before s_flag is reused
-          // pieces from the fixed shares: one per CTA whose share overlaps the pair's static blocks
-          const int nc = seq_nc(st_b), ns = st_nb - nc * cd;
-          long long sp0 = 0;
+          // pieces from the fixed shares: one per CTA whose share overlaps the pair's fixed blocks
+          const int ns = st_nb - seq_nc(st_b) * cd;
+          int sp0 = 0;
           for (int bb = 0; bb < st_b; ++bb) sp0 += seq_ns(bb);
-          sp0 = sp0 * Hkv + (long long)st_kvh * ns;
-          const int i0 = (int)(sp0 / share), i1 = (int)((sp0 + ns - 1) / share);
+          sp0 = sp0 * Hkv + st_kvh * ns;
+          const int i0 = sp0 / share, i1 = (sp0 + ns - 1) / share;
           const int n_fixed = i1 - i0 + 1;
           for (int i = tid; i < n_fixed; i += kThreads) s_list[i] = (i0 + i) * 2 + (i == 0 ? 1 : 0);
           if (tid == 0) s_flag = n_fixed;
           __syncthreads();
-          // pieces parked by CTAs that helped out of this pair's pool
-          const int hb = nc > 0 ? s_hb[st_b] + st_kvh * nc : 0;
-          for (int c = tid; c < nc; c += kThreads) {
-            if (ld_relaxed(helper_flag + hb + c) != 0) {
-              const int k = atomicAdd(&s_flag, 1);
-              if (k < kMaxList) s_list[k] = 2 * G + hb + c;
-              helper_flag[hb + c] = 0;                     // ready for the next launch
+          // pieces parked by CTAs that came over from other pairs
+          if (dyn_on) {
+            const int n_slots = min(G * kGqaMaxVisits, p.max_helper);
+            for (int i = tid; i < n_slots; i += kThreads) {
+              if (ld_relaxed(helper_pair + i) == pair + 1) {
+                const int k = atomicAdd(&s_flag, 1);
+                if (k < kMaxList) s_list[k] = 2 * G + i;
+                helper_pair[i] = 0;                        // ready for the next launch
+              }
             }
+            __syncthreads();
           }
-          __syncthreads();
           const int n_pieces = min(s_flag, kMaxList);
           fold_pieces(FoldArgs{p.part_o, p.part_lse, p.o, p.lse, Hq, p.lse_base2}, s_list, n_pieces, st_b, st_kvh, group,
                       warp, lane);
@@ -682,14 +719,14 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
         if ((++spins & 255u) == 0u && now_ns() > grace) break;
       }
     }
-  } else if (dyn_on) {
+  } else if (dyn_on && warp == 0) {
     // the last CTA to leave re-arms the pools for the next launch: nobody draws or probes any more
-    __syncthreads();
-    if (tid == 0) s_flag = (atom_add_acq_rel(exit_ctr, 1) == G - 1);
-    __syncthreads();
-    if (s_flag) {
-      for (int i = tid; i < P; i += kThreads) pool_ctr[i] = 0;
-      if (tid == 0) *exit_ctr = 0;
+    int last = 0;
+    if (lane == 0) last = (atom_add_acq_rel(exit_ctr, 1) == G - 1);
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      for (int i = lane; i < P; i += 32) pool_ctr[i] = 0;
+      if (lane == 0) *exit_ctr = 0;
     }
   }
 
@@ -698,11 +735,11 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
     unsigned long long* tr = p.trace + (size_t)blockIdx.x * 8;
     tr[0] = t_entry;
-    tr[1] = (t_first << 8) | (unsigned long long)(smid & 0xffu);   // low byte: SM id
-    tr[2] = t_static;
+    tr[1] = smid;
+    tr[2] = t_static;      // warp 0 left the fixed share for the pool (0: never)
     tr[3] = now_ns();
-    tr[4] = t_dyn;
-    tr[5] = (unsigned long long)n_drawn | ((unsigned long long)n_visits << 32);
+    tr[4] = t_dyn;         // end of the last segment's streaming
+    tr[5] = (unsigned long long)n_drawn | ((unsigned long long)n_visits << 32);   // warp 0's chunks, CTA's helper pieces
   }
 
   // sequences without any token: output 0, LSE -inf (CTA 0 sweeps them)
@@ -733,16 +770,10 @@ void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int p
   p->max_helper = std::min(std::max(max_helper, 0), kGqaMaxHelper);
   p->dyn_min_blocks = 64;
   // a dynamic tail only pays when a CTA's fixed share is long compared with a chunk
-  int pct = (blocks / std::max(p->ctas, 1) >= 96 && p->B <= kGqaSeqTable) ? 12 : 0;
-  if (pct_override >= 0) pct = std::min(pct_override, 50);
-  int chunk = chunk_override > 0 ? chunk_override : 8;
-  if (pct > 0 && p->max_helper > 0) {
-    // never more chunks than helper slots, whatever the sequence lengths turn out to be
-    const long long worst = (long long)p->B * p->Hkv * ((long long)nb * pct / 100);
-    while ((worst + chunk - 1) / chunk > p->max_helper) chunk += 4;
-  } else {
-    pct = 0;
-  }
+  int pct = (blocks / std::max(p->ctas, 1) >= 96 && p->B <= kGqaSeqTable) ? 30 : 0;
+  if (pct_override >= 0) pct = std::min(pct_override, 90);
+  int chunk = chunk_override > 0 ? chunk_override : 2;
+  if (p->max_helper < p->ctas * kGqaMaxVisits) pct = 0;    // every CTA needs its helper slots
   p->dyn_pct = pct;
   p->dyn_chunk = chunk;
 }
@@ -750,7 +781,8 @@ void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int p
 cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t stream) {
   if (p.B <= 0) return cudaSuccess;
   if (p.Hq % p.Hkv != 0 || p.Hq / p.Hkv > 8 || p.page_size % kBlockTok != 0 || p.ctas < 1 || p.ctas > kGqaMaxCtas ||
-      p.max_helper < 0 || p.max_helper > kGqaMaxHelper || p.dyn_pct < 0 || p.dyn_pct > 50)
+      p.max_helper < 0 || p.max_helper > kGqaMaxHelper || p.dyn_pct < 0 || p.dyn_pct > 90 ||
+      (p.dyn_pct > 0 && (p.dyn_chunk < 1 || p.max_helper < p.ctas * kGqaMaxVisits)))
     return cudaErrorInvalidValue;
   static bool attr_set[64] = {false};
   int dev = 0;
