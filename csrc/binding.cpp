@@ -14,6 +14,7 @@
 #include <string>
 
 #include "exchange.h"
+#include "lse_combine.h"
 #include "fifo.cuh"
 #include "ll128.cuh"
 #include "vmm_workspace.h"
@@ -165,6 +166,60 @@ std::tuple<torch::Tensor, torch::Tensor> alltoall_helix_native(torch::Tensor par
   return alltoall_impl(partial_o, softmax_stats, workspace, cp_rank, cp_size, false, 0, 0);
 }
 
+// ---- stand-alone LSE combine -------------------------------------------------------------------------
+// rank_dim 0: outputs [N, ..., D], lses [N, ...];  rank_dim -2: outputs [..., N, D], lses [..., N] (the layout
+// `alltoall` returns; lses may be a strided view such as recv_stats[..., 0]).  Result [..., D] (+ global LSE).
+std::tuple<torch::Tensor, torch::Tensor> lse_combine(torch::Tensor outputs, torch::Tensor lses, int64_t rank_dim,
+                                                     bool return_lse, bool base2) {
+  TORCH_CHECK(outputs.is_cuda() && lses.is_cuda(), "inputs must be on CUDA");
+  TORCH_CHECK(outputs.scalar_type() == at::ScalarType::Half || outputs.scalar_type() == at::ScalarType::BFloat16,
+              "outputs must be half or bfloat16");
+  TORCH_CHECK(lses.scalar_type() == at::ScalarType::Float, "lses must be float32");
+  TORCH_CHECK(rank_dim == 0 || rank_dim == -2, "rank_dim must be 0 ([N, ..., D]) or -2 ([..., N, D])");
+  TORCH_CHECK(outputs.dim() >= 2 && lses.dim() == outputs.dim() - 1, "outputs [.., D] needs lses with one dim less");
+  outputs = outputs.contiguous();
+  const int64_t D = outputs.size(-1), es = outputs.element_size();
+  TORCH_CHECK(D * es % 16 == 0 && D * es <= 2048, "row size must be a multiple of 16 bytes, at most 2048");
+  const int64_t N = rank_dim == 0 ? outputs.size(0) : outputs.size(-2);
+  int64_t rows = 1;
+  std::vector<int64_t> shape, lshape;
+  for (int i = 0; i < outputs.dim() - 1; ++i) {
+    const bool is_rank = (rank_dim == 0 && i == 0) || (rank_dim == -2 && i == outputs.dim() - 2);
+    TORCH_CHECK(lses.size(i) == outputs.size(i), "lses must match the leading dims of outputs");
+    if (is_rank) continue;
+    rows *= outputs.size(i);
+    shape.push_back(outputs.size(i));
+    lshape.push_back(outputs.size(i));
+  }
+  shape.push_back(D);
+  // LSEs as [N, rows] or [rows, N] with arbitrary (uniform) strides: flatten through a contiguous copy only if needed
+  torch::Tensor l2 = rank_dim == 0 ? lses.reshape({N, rows}) : lses.reshape({rows, N});
+  c10::cuda::CUDAGuard guard(outputs.device());
+  torch::Tensor out = torch::empty(shape, outputs.options());
+  torch::Tensor lse_out = return_lse ? torch::empty(lshape, lses.options()) : torch::empty({0}, lses.options());
+  helix::LseCombineParams p{};
+  p.o = reinterpret_cast<const uint8_t*>(outputs.data_ptr());
+  p.lse = reinterpret_cast<const uint8_t*>(l2.data_ptr());
+  p.out = reinterpret_cast<uint8_t*>(out.data_ptr());
+  p.lse_out = return_lse ? lse_out.data_ptr<float>() : nullptr;
+  if (rank_dim == 0) {
+    p.o_sn = rows * D * es; p.o_sr = D * es;
+    p.l_sn = l2.stride(0) * 4; p.l_sr = l2.stride(1) * 4;
+  } else {
+    p.o_sn = D * es; p.o_sr = N * D * es;
+    p.l_sn = l2.stride(1) * 4; p.l_sr = l2.stride(0) * 4;
+  }
+  p.out_sr = D * es;
+  p.rows = rows;
+  p.n = (int)N;
+  p.row_bytes = (int)(D * es);
+  p.is_bf16 = outputs.scalar_type() == at::ScalarType::BFloat16;
+  p.base2 = base2 ? 1 : 0;
+  cudaError_t e = helix::launch_lse_combine(p, env_pdl(), at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "helix: lse_combine launch failed: ", cudaGetErrorString(e));
+  return std::make_tuple(out, lse_out);
+}
+
 // ---- fused exchange + LSE combine ------------------------------------------------------------------
 // layout 0 ("native"): attn_out [B, H, D], stats [B, H] (LSE) or [B, H, 2]; result [B, H/cp, D]
 // layout 1 ("entries"): partial_o [..., cp, D], stats [..., cp, 2]; result [..., D]
@@ -305,6 +360,8 @@ TORCH_LIBRARY(helix_a2a_b200, m) {
       "return_lse, bool base2, int stats_mode, bool emulate, int skip_peer_mask, int timeout_ms) -> (Tensor, Tensor)",
       &alltoall_combine);
   m.def("read_status(Tensor workspace, int cp_rank, int cp_size) -> Tensor", &read_status);
+  m.def("lse_combine(Tensor outputs, Tensor lses, int rank_dim, bool return_lse, bool base2) -> (Tensor, Tensor)",
+        &lse_combine);
   register_compute_ops(m);
 }
 

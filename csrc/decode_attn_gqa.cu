@@ -43,13 +43,13 @@ using namespace sm100;
 
 constexpr int kD = 128;           // head dim
 constexpr int kBlockTok = 16;     // tokens per KV block (one MMA k-step of P V)
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 3;
 constexpr int kTileBytes = kBlockTok * kD * 2;        // 4096: one K (or V) block
 constexpr int kStageBytes = 2 * kTileBytes;           // K + V
-constexpr int kSmemPipe = kWarps * kStages * kStageBytes;   // 98304
-constexpr int kMergeBytes = kWarps * 4 * kD * 4;        // 8192: warps' partial O of four heads / piece list of a fold
+constexpr int kSmemPipe = kWarps * kStages * kStageBytes;   // 196608
+constexpr int kMergeBytes = kWarps * 4 * kD * 4;        // 16384: warps' partial O of four heads / piece list of a fold
 constexpr int kSmemBytes = kSmemPipe + kMergeBytes + 1024;   // + alignment slack
 constexpr int kMaxList = kMergeBytes / 4;               // pieces one fold can list
 static_assert(2 * kGqaMaxCtas <= kMaxList, "a fold lists at most one fixed piece and one helper piece per CTA");
@@ -87,9 +87,9 @@ __device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
 }
 
 // The CTA whose piece completed a pair folds all pieces listed in s_list (piece slots) into the final output.
-// Warp w folds heads 2w and 2w + 1 together: lanes first share out the pieces' weights, then every lane sums
-// four columns of both heads with sixteen independent 16-byte loads in flight.  Kept out of line so that its
-// registers do not weigh on the streaming loop.
+// Warp w folds head w: lanes first share out the pieces' weights, then every lane sums four columns with
+// sixteen independent 16-byte loads in flight.  Kept out of line so that its registers do not weigh on the
+// streaming loop.
 struct FoldArgs {
   const float* part_o;
   const float* part_lse;
@@ -99,96 +99,66 @@ struct FoldArgs {
 };
 __device__ __noinline__ void fold_pieces(FoldArgs p, const int* s_list, int n_pieces, int st_b, int st_kvh, int group,
                                          int warp, int lane) {
-  const int Hq = p.Hq;
-  {
-    const int h0 = warp * 2, h1 = warp * 2 + 1;
-    const bool has1 = h1 < group;
-    if (h0 < group) {
-      float M0 = -INFINITY, M1 = -INFINITY;
-      for (int i = lane; i < n_pieces; i += 32) {
-        const float* pl = p.part_lse + (size_t)s_list[i] * 8;
-        M0 = fmaxf(M0, __ldcg(pl + h0));
-        if (has1) M1 = fmaxf(M1, __ldcg(pl + h1));
-      }
+  for (int hg = warp; hg < group; hg += kWarps) {
+    float M = -INFINITY;
+    for (int i = lane; i < n_pieces; i += 32) M = fmaxf(M, __ldcg(p.part_lse + (size_t)s_list[i] * 8 + hg));
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        M0 = fmaxf(M0, __shfl_xor_sync(0xffffffffu, M0, o));
-        M1 = fmaxf(M1, __shfl_xor_sync(0xffffffffu, M1, o));
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c0 = 0; c0 < n_pieces; c0 += 32) {
+      const int i = c0 + lane;
+      float w = 0.f;
+      int my_slot = 0;
+      if (i < n_pieces) {
+        my_slot = s_list[i];
+        if (M != -INFINITY) w = fast_exp2(__ldcg(p.part_lse + (size_t)my_slot * 8 + hg) - M);
       }
-      float L0 = 0.f, L1 = 0.f;
-      float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int c0 = 0; c0 < n_pieces; c0 += 32) {
-        const int i = c0 + lane;
-        float w0 = 0.f, w1 = 0.f;
-        int my_slot = 0;
-        if (i < n_pieces) {
-          my_slot = s_list[i];
-          const float* pl = p.part_lse + (size_t)my_slot * 8;
-          if (M0 != -INFINITY) w0 = fast_exp2(__ldcg(pl + h0) - M0);
-          if (has1 && M1 != -INFINITY) w1 = fast_exp2(__ldcg(pl + h1) - M1);
-        }
-        L0 += w0;
-        L1 += w1;
-        const int nbatch = min(32, n_pieces - c0);
-        for (int j0 = 0; j0 < nbatch; j0 += 8) {
-          float4 v0[8], v1[8];
+      L += w;
+      const int nbatch = min(32, n_pieces - c0);
+      for (int j0 = 0; j0 < nbatch; j0 += 16) {
+        float4 v[16];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (j0 + j < nbatch) {
-              const int sl = __shfl_sync(0xffffffffu, my_slot, j0 + j);
-              const float4* po = reinterpret_cast<const float4*>(p.part_o + (size_t)sl * 8 * kD);
-              v0[j] = __ldcg(po + h0 * (kD / 4) + lane);
-              if (has1) v1[j] = __ldcg(po + h1 * (kD / 4) + lane);
-            }
+        for (int j = 0; j < 16; ++j) {
+          if (j0 + j < nbatch) {
+            const int sl = __shfl_sync(0xffffffffu, my_slot, j0 + j);
+            v[j] = __ldcg(reinterpret_cast<const float4*>(p.part_o + ((size_t)sl * 8 + hg) * kD) + lane);
           }
+        }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (j0 + j < nbatch) {
-              const float x0 = __shfl_sync(0xffffffffu, w0, j0 + j);
-              const float x1 = __shfl_sync(0xffffffffu, w1, j0 + j);
-              a0.x += x0 * v0[j].x;
-              a0.y += x0 * v0[j].y;
-              a0.z += x0 * v0[j].z;
-              a0.w += x0 * v0[j].w;
-              if (has1) {
-                a1.x += x1 * v1[j].x;
-                a1.y += x1 * v1[j].y;
-                a1.z += x1 * v1[j].z;
-                a1.w += x1 * v1[j].w;
-              }
-            }
+        for (int j = 0; j < 16; ++j) {
+          if (j0 + j < nbatch) {
+            const float x = __shfl_sync(0xffffffffu, w, j0 + j);
+            acc.x += x * v[j].x;
+            acc.y += x * v[j].y;
+            acc.z += x * v[j].z;
+            acc.w += x * v[j].w;
           }
         }
       }
+    }
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        L0 += __shfl_xor_sync(0xffffffffu, L0, o);
-        L1 += __shfl_xor_sync(0xffffffffu, L1, o);
-      }
-      auto store_head = [&](int hg, float M, float L, const float4& a) {
-        const float inv = L > 0.f ? 1.f / L : 0.f;
-        const int h = st_kvh * group + hg;
-        uint2 packed;
-        packed.x = pack_bf16(a.x * inv, a.y * inv);
-        packed.y = pack_bf16(a.z * inv, a.w * inv);
-        *reinterpret_cast<uint2*>(p.o + ((int64_t)st_b * Hq + h) * kD + lane * 4) = packed;
-        if (lane == 0) {
-          const float lse2 = L > 0.f ? M + log2f(L) : -INFINITY;
-          p.lse[(int64_t)st_b * Hq + h] = p.lse_base2 ? lse2 : lse2 * kLn2;
-        }
-      };
-      store_head(h0, M0, L0, a0);
-      if (has1) store_head(h1, M1, L1, a1);
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const int h = st_kvh * group + hg;
+    uint2 packed;
+    packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+    packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(p.o + ((int64_t)st_b * p.Hq + h) * kD + lane * 4) = packed;
+    if (lane == 0) {
+      const float lse2 = L > 0.f ? M + log2f(L) : -INFINITY;
+      p.lse[(int64_t)st_b * p.Hq + h] = p.lse_base2 ? lse2 : lse2 * kLn2;
     }
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_constant__ GqaDecodeParams p) {
+__global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_constant__ GqaDecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kWarps][kStages];
   __shared__ float s_m[kWarps][8], s_l[kWarps][8];
   __shared__ int s_flag;                         // CTA-wide broadcast word (last arrival, scan result, list length)
   __shared__ int s_dynblk[2];                    // pool blocks the warps streamed in this segment (two slots, alternating)
+  __shared__ int s_cursor[2];                    // next block of the segment's fixed range to hand to a warp (alternating)
   __shared__ int s_nb[kGqaSeqTable];             // KV blocks of each sequence
   __shared__ unsigned short s_nc[kGqaSeqTable];  // chunks in each of its pairs' pools
 
@@ -207,6 +177,8 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
     tma_prefetch_desc(&p.v_map);
     s_dynblk[0] = 0;
     s_dynblk[1] = 0;
+    s_cursor[0] = 0;
+    s_cursor[1] = 0;
   }
   const bool early_kv = p.kv_stable != 0;
   if (!early_kv) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -266,8 +238,9 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
   bool ok = true;
 
   // ---- segments: blocks of one pair that this CTA streams in one go ---------------------------------
-  // [kb_begin, kb_end) are blocks of the fixed share (warp w takes kb_begin + w, + W, ...); with `pool` the warps
-  // then go on drawing chunks of cd blocks from the pair's pool until it is empty.
+  // [kb_begin, kb_end) are blocks of the fixed share, handed to the warps one at a time through a cursor in
+  // shared memory (warps do not stream equally fast either); with `pool` the warps then go on drawing chunks of
+  // cd blocks from the pair's pool until it is empty.
   struct Seg {
     int b, kvh, kb_begin, kb_end, n_blocks, seq_len;
     int slot;                // piece slot, should this segment open a new running state
@@ -350,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
 
   // ---- per-warp loader: which block comes next, and the loads in flight -------------------------------
   int ld_mode = 2;           // 0: blocks of the fixed share, 1: chunks drawn from the pool, 2: nothing more
-  int ld_kb = 0, ld_end = 0, ld_kvh = 0, ld_nc = 0, ld_ns = 0;
+  int ld_base = 0, ld_len = 0, ld_kvh = 0, ld_nc = 0, ld_ns = 0, ld_par = 0;
   bool ld_pool = false;
   const int32_t* ld_bt = p.block_table;
   int* ld_ctr = pool_ctr;
@@ -363,9 +336,11 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
   auto gen_advance = [&]() {
     pend_valid = false;
     if (ld_mode == 0) {
-      if (ld_kb < ld_end) {
-        pend_kb = ld_kb;
-        ld_kb += kWarps;
+      int i = 0;
+      if (lane == 0) i = atomicAdd(&s_cursor[ld_par], 1);
+      i = __shfl_sync(0xffffffffu, i, 0);
+      if (i < ld_len) {
+        pend_kb = ld_base + i;
         pend_valid = true;
       } else {
         ld_mode = ld_pool ? 1 : 2;
@@ -418,8 +393,9 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
   // being merged, so the ramp of one segment hides behind the epilogue of the one before.
   auto seg_begin = [&](const Seg& sg) {
     ld_mode = 0;
-    ld_kb = sg.kb_begin + warp;
-    ld_end = sg.kb_end;
+    ld_par ^= 1;
+    ld_base = sg.kb_begin;
+    ld_len = sg.kb_end - sg.kb_begin;
     ld_kvh = sg.kvh;
     ld_pool = sg.pool;
     ld_nc = seq_nc(sg.b);
@@ -591,7 +567,10 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
       if (q >= 0) nxt = pool_seg(q);
     }
     if (nxt.valid) seg_begin(nxt);
-    if (tid == 0) s_dynblk[dpar] = 0;     // the next use of this slot is two barriers away
+    if (tid == 0) {                       // the next use of these slots is two barriers away
+      s_dynblk[dpar] = 0;
+      s_cursor[dpar] = 0;
+    }
 
     const bool leave = !nxt.valid || nxt.b != st_b || nxt.kvh != st_kvh;
     if (leave && st_blocks == 0) st_active = false;      // a pool that turned out to be empty: nothing to park
@@ -756,11 +735,11 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
 
 }  // namespace
 
-// Number of CTAs for a launch: two per SM, but never so many that a CTA streams fewer than
-// 32 blocks (its fixed ramp + merge cost is worth about that much streaming).
+// Number of CTAs for a launch: one per SM (eight warps each), but never so many that a CTA streams fewer than
+// 64 blocks (its fixed ramp + merge cost is worth about that much streaming).
 int gqa_pick_ctas(int B, int Hkv, int max_seq_len, int sm_count) {
   const long long blocks = (long long)std::max(B, 1) * Hkv * std::max((max_seq_len + kBlockTok - 1) / kBlockTok, 1);
-  long long ctas = std::min<long long>(2LL * sm_count, std::max<long long>(blocks / 32, 1));
+  long long ctas = std::min<long long>(sm_count, std::max<long long>(blocks / 64, 1));
   return (int)std::min<long long>(ctas, kGqaMaxCtas);
 }
 
@@ -770,7 +749,8 @@ void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int p
   p->max_helper = std::min(std::max(max_helper, 0), kGqaMaxHelper);
   p->dyn_min_blocks = 64;
   // a dynamic tail only pays when a CTA's fixed share is long compared with a chunk
-  int pct = (blocks / std::max(p->ctas, 1) >= 96 && p->B <= kGqaSeqTable) ? 30 : 0;
+  int pct = 0;   // fixed shares unless the caller asks otherwise
+  (void)blocks;
   if (pct_override >= 0) pct = std::min(pct_override, 90);
   int chunk = chunk_override > 0 ? chunk_override : 2;
   if (p->max_helper < p->ctas * kGqaMaxVisits) pct = 0;    // every CTA needs its helper slots

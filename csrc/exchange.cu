@@ -46,6 +46,7 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_kernel(const __grid_con
   pdl_launch_dependents();
   Ctx cx = make_ctx(p, &ctl, rank, blockIdx.x);
   cx.deadline = globaltimer_ns() + p.timeout_ns;
+  load_ring_heads(p, cx);
 
   if (warp < NS) {
     sender_warp<NIT>(p, cx, io, warp, NS, lane);

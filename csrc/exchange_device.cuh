@@ -68,6 +68,9 @@ HELIX_D void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_depen
 struct Control {
   int abort;
   unsigned done;
+  // Line count of every outgoing ring at kernel entry, read ONCE per CTA before the warps split into roles:
+  // several sender warps may share a ring, and the one that finishes first stores the new count.
+  unsigned long long head[kMaxCp];
 };
 
 struct Ctx {
@@ -293,7 +296,7 @@ HELIX_D void sender_warp(const ExchangeParams& p, const Ctx& cx, const RankIO& i
     if ((p.skip_peer_mask >> peer) & 1u) continue;
     uint8_t* ring = cx.ws + (int64_t)peer * cx.stride + ring_offset(cx.lay, rank, c);
     uint8_t* sinfo = cx.my_row + sinfo_slot(cx.lay, peer, c);
-    const uint64_t head = ld_volatile_8(sinfo + kSinfoHeadOff);
+    const uint64_t head = cx.ctl->head[peer];
     uint64_t tail = ld_volatile_8(sinfo + kSinfoTailOff);
     bool ok = true;
     uint64_t lo[NIT], hi[NIT];
@@ -536,6 +539,13 @@ HELIX_D void receiver_combine_warp(const ExchangeParams& p, const Ctx& cx, const
         reinterpret_cast<float*>(io.st_dst)[e] = gl;
       }
       hook(e, lane);
+    } else if (k == 0 && have) {
+      // this call gave up on a wait: leave NaN in the row instead of whatever the buffer held, so that a
+      // caller who does not read the status block still cannot mistake the row for a result
+      const uint64_t nan4 = BF16 ? 0x7FC07FC07FC07FC0ull : 0x7E007E007E007E00ull;
+      uint8_t* od = io.o_dst + e * p.od_se;
+      for (int w = lane; w < (p.o_bytes >> 3); w += 32) st_8(od + 8 * w, nan4);
+      if (io.st_dst != nullptr && lane == 0) reinterpret_cast<float*>(io.st_dst)[e] = __uint_as_float(0x7FC00000u);
     }
     if (p.rounds_per_publish > 0 && (rd + 1) % p.rounds_per_publish == 0 && rd + 1 < rounds) {
       named_barrier(kAllRecvBarrier, NR * 32);
@@ -543,6 +553,14 @@ HELIX_D void receiver_combine_warp(const ExchangeParams& p, const Ctx& cx, const
     }
   }
   finish_receiver(p, cx, rtail0, n_mine, L, NR, lane);
+}
+
+// Fills ctl->head for the CTA's channel; every thread of the CTA must call it (it ends with a CTA barrier).
+HELIX_D void load_ring_heads(const ExchangeParams& p, const Ctx& cx) {
+  const int peer = (int)threadIdx.x;
+  if (peer < p.cp_size && peer != cx.rank)
+    cx.ctl->head[peer] = ld_volatile_8(cx.my_row + sinfo_slot(cx.lay, peer, cx.channel) + kSinfoHeadOff);
+  __syncthreads();
 }
 
 HELIX_D Ctx make_ctx(const ExchangeParams& p, Control* ctl, int rank, int channel) {

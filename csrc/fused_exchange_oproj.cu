@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
     pdl_launch_dependents();
     Ctx cx = make_ctx(p, &ctl, rank, blockIdx.x);
     cx.deadline = globaltimer_ns() + p.timeout_ns;
+    load_ring_heads(p, cx);
     if (warp < NS) {
       sender_warp<NIT>(p, cx, io, warp, NS, lane);
     } else {
@@ -86,6 +87,10 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
       gp, dyn_smem, gidx / gp.splits, gidx % gp.splits, threadIdx.x,
       [] { named_barrier(kGemmBarrier, oproj_dev::kThreads); },
       [&](unsigned long long deadline) {
+        // The counters below are shared by all launches and re-armed by the previous one: under programmatic
+        // launch this CTA may be resident while that launch still runs, so wait for it first (x depends on the
+        // kernel before us anyway; the weight stages were requested above).
+        pdl_wait();
         // rows written by the combine warps (generic proxy, other SMs) must be complete before TMA reads them
         unsigned spins = 0;
         while (true) {

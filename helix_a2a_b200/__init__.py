@@ -8,6 +8,7 @@ fused paths)::
     init_workspace(workspace, cp_rank, cp_size) -> None
     alltoall(partial_o, softmax_stats, workspace, cp_rank, cp_size) -> (Tensor, Tensor)
     alltoall_combine(attn_out, lse, workspace, cp_rank, cp_size, ...) -> Tensor
+    lse_combine(outputs, lses, ...) -> Tensor                 # stand-alone combine kernel
     check_status / reset_workspace / debug_info
 """
 from ._version import __version__
@@ -21,6 +22,7 @@ from .api import (
     debug_info,
     init_workspace,
     init_workspace_all_rows,
+    lse_combine,
     reset_workspace,
     workspace_size,
 )
@@ -32,6 +34,7 @@ __all__ = [
     "alltoall",
     "alltoall_combine",
     "alltoall_combine_oproj",
+    "lse_combine",
     "check_status",
     "reset_workspace",
     "debug_info",

@@ -191,6 +191,33 @@ def alltoall_combine_oproj(attn_out: torch.Tensor, lse: torch.Tensor, w_o: torch
         return _oproj.oproj(x.reshape(B, -1), w_o)
 
 
+def lse_combine(outputs: torch.Tensor, lses: torch.Tensor, *, return_lse: bool = False, base2: bool = False,
+                layout: str = "NBHD"):
+    """LSE-weighted combine of per-rank partial attention outputs that are already on this rank.
+
+    ``layout="NBHD"``: ``outputs [N, ..., D]`` with ``lses [N, ...]`` (what two NCCL all-to-alls leave);
+    ``layout="BHND"``: ``outputs [..., N, D]`` with ``lses [..., N]`` (what :func:`alltoall` returns; pass
+    ``recv_stats[..., 0]``).  Returns ``[..., D]`` in the input dtype, plus the global LSE with ``return_lse``.
+    NaN and infinite LSEs count as "no contribution"; a row without any contribution is zero with LSE ``-inf``.
+
+    On CUDA tensors this is one hand-written kernel (``csrc/lse_combine.cu``), the counterpart of the
+    reference's Triton ``dcp_lse_combine_triton`` (``patches/dcp_alltoall_helix.py:210-384``); the fused
+    :func:`alltoall_combine` does the same arithmetic while the rows arrive and needs no separate call.
+    """
+    if layout not in ("NBHD", "BHND"):
+        raise ValueError("layout must be 'NBHD' or 'BHND'")
+    if not outputs.is_cuda:
+        o = outputs if layout == "NBHD" else outputs.movedim(-2, 0)
+        l = lses if layout == "NBHD" else lses.movedim(-1, 0)
+        res = rm.lse_combine(o, l, return_lse=return_lse, base2=base2)
+        if return_lse:
+            return res[0].to(outputs.dtype), res[1]
+        return res.to(outputs.dtype)
+    from .ops._ext import ops
+    out, g = ops().lse_combine(outputs, lses.float(), 0 if layout == "NBHD" else -2, return_lse, base2)
+    return (out, g) if return_lse else out
+
+
 def check_status(workspace: torch.Tensor, cp_rank: int, cp_size: int, *, raise_on_error: bool = True) -> dict:
     """Read the status block of the local row (synchronises the current stream)."""
     if isinstance(workspace, CpuWorkspace):

@@ -8,12 +8,19 @@ module it replaces in vLLM 0.22 (``vllm/v1/attention/ops/dcp_alltoall.py``)::
     dcp_a2a_ensure_initialized(cp_group)     # before CUDA-graph capture
 
 Backend switch, read at import like the reference (``patches/dcp_alltoall_helix.py:40,49``):
-``HELIX_A2A_BACKEND=nccl`` (default) is two ``all_to_all_single`` + a torch combine
-(``HELIX_A2A_NCCL_IMPL=stock`` calls the function of the replaced vLLM module instead); ``native`` runs ONE kernel that
+``HELIX_A2A_BACKEND=nccl`` (default) is two ``all_to_all_single`` + the stand-alone combine kernel
+(``dcp_lse_combine``; ``HELIX_A2A_NCCL_IMPL=stock`` calls the function of the replaced vLLM module instead);
+``native`` runs ONE kernel that
 reads ``cp_attn_out`` / ``cp_attn_lse`` in place (no permute / pad / zeros copies), exchanges over
 NVLink and applies the LSE-weighted combine on the receive side.  Base-2 LSEs (FlashInfer) are
 combined natively instead of being converted to base e and back
 (``patches/dcp_alltoall_helix.py:564-567,591-593``).
+
+A device-side wait that runs out of time does not hang the GPU: the kernel records a status, fills the rows it
+could not complete with NaN and returns.  ``dcp_a2a_check_status()`` turns that status into a
+``HelixTimeoutError``; the import hook calls it after every engine step, so a failed exchange stops the
+server instead of serving garbage.  The waits of this hook default to 30 s (``HELIX_A2A_HOOK_TIMEOUT_MS``):
+ranks may be far apart during warm-up.
 
 ``apply_runtime_patch()`` swaps the function into the vLLM modules that imported it; the
 ``install`` module next to this file rewrites vLLM's file on disk instead.
@@ -36,6 +43,7 @@ _HELIX_BACKEND = os.environ.get("HELIX_A2A_BACKEND", "nccl").lower()
 # What "nccl" means: "own" = two all_to_all_single + a torch combine, as in the reference's hook
 # (patches/dcp_alltoall_helix.py:455-504); "stock" = the function of the vLLM module this hook replaced.
 _NCCL_IMPL = os.environ.get("HELIX_A2A_NCCL_IMPL", "own").lower()
+_HOOK_TIMEOUT_MS = max(int(os.environ.get("HELIX_A2A_HOOK_TIMEOUT_MS", "30000") or 30000), 1)
 _workspace: Optional[torch.Tensor] = None
 _workspace_key = None
 _stock_reduce = None     # vLLM's original function, when it could be imported
@@ -48,6 +56,28 @@ def _lse_weighted_combine(outputs, lses, return_lse: bool = False, is_lse_base_o
     if return_lse:
         return res[0].to(outputs.dtype), res[1]
     return res.to(outputs.dtype)
+
+
+def dcp_lse_combine(recv_output: torch.Tensor, recv_lse: torch.Tensor, return_lse: bool = False,
+                    is_lse_base_on_e: bool = True):
+    """``recv_output [N, B, H, D]`` + ``recv_lse [N, B, H]`` -> ``[B, H, D]`` (+ global LSE ``[B, H]``).
+
+    Same contract as the reference's ``dcp_lse_combine_triton`` (``patches/dcp_alltoall_helix.py:323-384``);
+    on CUDA tensors it is the library's hand-written combine kernel, on CPU tensors the torch oracle."""
+    return _helix.lse_combine(recv_output, recv_lse, return_lse=return_lse, base2=not is_lse_base_on_e)
+
+
+dcp_lse_combine_triton = dcp_lse_combine   # the reference's public name; there is no Triton behind it here
+
+
+def dcp_a2a_check_status(raise_on_error: bool = True) -> dict:
+    """Status of the native exchange on this rank (synchronises the current stream).  Raises
+    ``helix_a2a_b200.HelixTimeoutError`` if a device-side wait ran out since the workspace was (re)initialised;
+    the workspace then needs ``helix_a2a_b200.reset_workspace`` on every rank before it is used again."""
+    if _workspace is None or _workspace_key is None:
+        return {"code": 0, "name": "ok"}
+    cp_size, cp_rank, _ = _workspace_key
+    return _helix.check_status(_workspace, cp_rank, cp_size, raise_on_error=raise_on_error)
 
 
 def _mnnvl_setting():
@@ -116,7 +146,7 @@ def _nccl_reduce(cp_attn_out, cp_attn_lse, cp_group, return_lse, is_lse_base_on_
     w2 = dist.all_to_all_single(rl.view(-1), sl.view(-1), group=cp_group.device_group, async_op=True)
     w1.wait()
     w2.wait()
-    return _lse_weighted_combine(ro, rl, return_lse=return_lse, is_lse_base_on_e=is_lse_base_on_e)
+    return dcp_lse_combine(ro, rl, return_lse=return_lse, is_lse_base_on_e=is_lse_base_on_e)
 
 
 def dcp_a2a_lse_reduce(cp_attn_out: torch.Tensor, cp_attn_lse: torch.Tensor, cp_group, ctx=None,
@@ -130,7 +160,8 @@ def dcp_a2a_lse_reduce(cp_attn_out: torch.Tensor, cp_attn_lse: torch.Tensor, cp_
         ws = _get_workspace(rank, world, cp_group, cp_attn_out.device)
         lse = cp_attn_lse if cp_attn_lse.dtype == torch.float32 else cp_attn_lse.float()
         return _helix.alltoall_combine(cp_attn_out.contiguous(), lse.contiguous(), ws, rank, world,
-                                       return_lse=return_lse, base2=not is_lse_base_on_e)
+                                       return_lse=return_lse, base2=not is_lse_base_on_e,
+                                       timeout_ms=_HOOK_TIMEOUT_MS)
     if _stock_reduce is not None and _NCCL_IMPL == "stock":
         return _stock_reduce(cp_attn_out, cp_attn_lse, cp_group, ctx, return_lse, is_lse_base_on_e)
     return _nccl_reduce(cp_attn_out, cp_attn_lse, cp_group, return_lse, is_lse_base_on_e)

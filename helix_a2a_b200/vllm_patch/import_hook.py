@@ -6,7 +6,8 @@ with ``from ... import`` when they are first imported.  A meta-path finder gets 
 lets the stock module load, then swaps the two public functions before any backend sees them.
 It also wraps ``Worker.compile_or_warm_up_model`` so that the workspace exists before CUDA-graph
 capture starts (stock vLLM never calls ``dcp_a2a_ensure_initialized``; the reference asks the
-integrator to, ``patches/dcp_alltoall_helix.py:119-135``).
+integrator to, ``patches/dcp_alltoall_helix.py:119-135``), and ``Worker.execute_model`` so that the status
+of the native exchange is read after every step (``HELIX_A2A_HOOK_CHECK=0`` switches that off).
 
 ``install()`` works in the current process.  vLLM's worker processes are separate interpreters:
 put ``helix_a2a_b200/vllm_patch/autoload`` on ``PYTHONPATH`` (``autoload_env()`` returns the
@@ -50,6 +51,17 @@ def _patch_worker_module(module) -> None:
     compile_or_warm_up_model.__wrapped__ = warm
     worker.compile_or_warm_up_model = compile_or_warm_up_model
 
+    step = getattr(worker, "execute_model", None)
+    if step is not None and not getattr(step, "__helix_hooked__", False):
+        def execute_model(self, *args, **kwargs):
+            out = step(self, *args, **kwargs)
+            _check_after_step()
+            return out
+
+        execute_model.__helix_hooked__ = True
+        execute_model.__wrapped__ = step
+        worker.execute_model = execute_model
+
 
 def _ensure_before_capture() -> None:
     """Create the workspace while ranks are still in lock step (model loaded, nothing captured yet)."""
@@ -62,6 +74,17 @@ def _ensure_before_capture() -> None:
     except AssertionError:      # no DCP group in this deployment
         return
     hx.dcp_a2a_ensure_initialized(group)
+
+
+def _check_after_step() -> None:
+    """A device-side wait of the native exchange that ran out must stop the engine, not go on serving the
+    NaN rows it left: read the status block once per step (64 bytes, after the step's own synchronisation)."""
+    if os.environ.get("HELIX_A2A_BACKEND", "nccl").lower() != "native":
+        return
+    if os.environ.get("HELIX_A2A_HOOK_CHECK", "1").strip() == "0":
+        return
+    from helix_a2a_b200.vllm_patch import dcp_alltoall_helix as hx
+    hx.dcp_a2a_check_status(raise_on_error=True)
 
 
 class _PatchingLoader(importlib.abc.Loader):

@@ -199,6 +199,59 @@ def test_timeout_returns_status_and_gpu_stays_usable(helix):
     assert helix.check_status(ws, 1, cp)["code"] == 0
 
 
+def test_timeout_in_combine_mode_leaves_nan_rows_and_hook_raises(helix):
+    """Combine mode with a sender that stays silent: the rows that could not be completed come out as NaN
+    (never as stale memory) and the serving hook's status check raises."""
+    from helix_a2a_b200.vllm_patch import dcp_alltoall_helix as hook
+    cp, B, H, D = 2, 4, 16, 128
+    ws = _ws(helix, cp)
+    outs = torch.randn(cp, B, H, D, device="cuda").bfloat16()
+    lses = torch.randn(cp, B, H, device="cuda")
+    got, glse = _ops().alltoall_combine(outs, lses, ws, 0, cp, 0, True, False, 0, True, 0b10, 50)
+    torch.cuda.synchronize()
+    assert torch.isnan(got[1].float()).all() and torch.isnan(glse[1]).all()      # rank 1 never heard from rank 0
+    old = hook._workspace, hook._workspace_key
+    try:
+        hook._workspace, hook._workspace_key = ws, (cp, 1, "cuda")
+        with pytest.raises(helix.HelixTimeoutError):
+            hook.dcp_a2a_check_status()
+        assert hook.dcp_a2a_check_status(raise_on_error=False)["code"] == 1
+    finally:
+        hook._workspace, hook._workspace_key = old
+    helix.init_workspace_all_rows(ws, cp)
+    got, _ = _ops().alltoall_combine(outs, lses, ws, 0, cp, 0, False, False, 0, True, 0, 0)
+    from helix_a2a_b200.ops import reference_math as rm
+    assert (got.float() - rm.head_scatter_combine_reference(outs, lses)).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("N,B,H,D", [(2, 3, 8, 128), (8, 5, 16, 512), (4, 1, 4, 64), (3, 7, 2, 1024)])
+@pytest.mark.parametrize("base2", [False, True])
+def test_lse_combine_kernel_matches_fp32_reference(helix, dtype, N, B, H, D, base2):
+    """Stand-alone combine kernel against the torch oracle, both layouts, including the -inf / NaN rules."""
+    from helix_a2a_b200.ops import reference_math as rm
+    torch.manual_seed(N * 100 + D)
+    o = torch.randn(N, B, H, D, device="cuda").to(dtype)
+    l = torch.randn(N, B, H, device="cuda") * 3
+    l[0, 0, 0] = float("-inf")
+    l[1, 0, 1] = float("nan")
+    l[:, -1, -1] = float("-inf")                      # a row nobody contributes to
+    if N > 2:
+        l[2, 0, 0] = float("inf")
+    want, wl = rm.lse_combine(o.float(), l, return_lse=True, base2=base2)
+    got, gl = helix.lse_combine(o, l, return_lse=True, base2=base2)
+    assert got.dtype == dtype and got.shape == (B, H, D)
+    assert (got.float() - want).abs().max() < 2e-2
+    fin = torch.isfinite(wl)
+    assert (gl[fin] - wl[fin]).abs().max() < 1e-4 and torch.equal(torch.isfinite(gl), fin)
+    assert (got[-1, -1] == 0).all() and gl[-1, -1] == float("-inf")
+    # the layout `alltoall` returns: [..., N, D] with the LSE in slot 0 of the stats pair
+    ro = o.permute(1, 2, 0, 3).contiguous()
+    rs = torch.stack([l.permute(1, 2, 0), torch.zeros(B, H, N, device="cuda")], dim=-1).contiguous()
+    got2 = helix.lse_combine(ro, rs[..., 0], base2=base2, layout="BHND")
+    assert torch.equal(got2, got)
+
+
 def test_cuda_graph_replay(helix):
     from helix_a2a_b200.ops import reference_math as rm
     cp, B, H, D = 4, 8, 64, 128

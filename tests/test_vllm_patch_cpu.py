@@ -62,3 +62,51 @@ def test_installer_dry_run(tmp_path, capsys):
     assert (ops / "dcp_alltoall.py.orig").exists() and "helix_a2a_b200" in (ops / "dcp_alltoall.py").read_text()
     assert install.main(["--vllm-dir", str(tmp_path), "--uninstall"]) == 0
     assert (ops / "dcp_alltoall.py").read_text().startswith("def dcp_a2a")
+
+
+def test_hook_status_check_raises_and_combine_name_parity(monkeypatch):
+    """The serving hook turns a recorded device-side timeout into an exception; the reference's public
+    combine name exists and agrees with the oracle on CPU tensors."""
+    import helix_a2a_b200 as helix
+    from helix_a2a_b200.ops import reference_math as rm
+    from helix_a2a_b200.vllm_patch import dcp_alltoall_helix as hook
+    assert hook.dcp_a2a_check_status()["code"] == 0            # no workspace yet: nothing to report
+    monkeypatch.setattr(hook, "_workspace", object())
+    monkeypatch.setattr(hook, "_workspace_key", (2, 1, "cuda"))
+
+    def fake_status(ws, rank, size, raise_on_error=True):
+        assert (rank, size) == (1, 2)
+        if raise_on_error:
+            raise helix.HelixTimeoutError(1, 0, 3, 7)
+        return {"code": 1, "peer": 0, "channel": 3, "entry": 7}
+
+    monkeypatch.setattr(hook._helix, "check_status", fake_status)
+    with pytest.raises(helix.HelixTimeoutError):
+        hook.dcp_a2a_check_status()
+    assert hook.dcp_a2a_check_status(raise_on_error=False)["code"] == 1
+    o, l = torch.randn(3, 2, 4, 16), torch.randn(3, 2, 4)
+    got, gl = hook.dcp_lse_combine_triton(o, l, return_lse=True, is_lse_base_on_e=False)
+    want, wl = rm.lse_combine(o, l, return_lse=True, base2=True)
+    assert (got - want).abs().max() < 1e-6 and (gl - wl).abs().max() < 1e-6
+
+
+def test_import_hook_checks_status_after_each_step(monkeypatch):
+    """Worker.execute_model is wrapped so that a failed exchange stops the engine after the step it happened in."""
+    import types
+    from helix_a2a_b200.vllm_patch import import_hook, dcp_alltoall_helix as hook
+    calls = []
+
+    class Worker:
+        def compile_or_warm_up_model(self):
+            return "warm"
+
+        def execute_model(self, x):
+            return x + 1
+
+    mod = types.SimpleNamespace(Worker=Worker)
+    import_hook._patch_worker_module(mod)
+    monkeypatch.setenv("HELIX_A2A_BACKEND", "native")
+    monkeypatch.setattr(hook, "dcp_a2a_check_status", lambda raise_on_error=True: calls.append(raise_on_error))
+    assert Worker().execute_model(1) == 2 and calls == [True]
+    monkeypatch.setenv("HELIX_A2A_HOOK_CHECK", "0")
+    assert Worker().execute_model(1) == 2 and calls == [True]
