@@ -125,6 +125,69 @@ def barrier(world):
     torch.cuda.synchronize()
 
 
+def time_op_in_graph(fn, world: int, calls: int = 20, replays: int = 20) -> float:
+    """Microseconds per call of ``fn`` (a collective every rank calls), measured as a CUDA graph of ``calls``
+    back-to-back calls replayed ``replays`` times: device time without host launch overhead, max over ranks.
+    Both arms of the benchmark time their exchange + combine with this one function."""
+    import torch
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            fn()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(calls):
+                fn()
+    torch.cuda.current_stream().wait_stream(s)
+    for _ in range(3):
+        g.replay()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        g.replay()
+    e1.record()
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world) / (replays * calls) * 1e3
+
+
+def bench_config(n_layers: int, batch: int, ctx: int, world: int, page_size: int, local_ctx: int, kv_bytes: int,
+                 graph: bool) -> dict:
+    """The ``config`` entry of the JSON line: what is measured, with the same keys in both arms (how each arm
+    computes it goes under ``extras.path``)."""
+    return {"model": f"llama3-70b-arch attention stack ({n_layers} layers, 64q/8kv heads, d=128, hidden 8192)",
+            "global_batch": batch, "seq_len": ctx, "parallelism": f"cp{world}", "page_size": page_size,
+            "kv_tokens_per_gpu_per_seq": local_ctx,
+            "l2": "inputs larger than L2 (KV cache read per step: %.1f GB per GPU)" % (kv_bytes / 1e9),
+            "cuda_graph": graph}
+
+
+def check_exchange_against_nccl(stack, q_layer0, rank: int, world: int, group) -> float:
+    """One layer's exchange + combine on every rank against two NCCL all-to-alls + the fp32 torch combine.
+    Returns the largest absolute difference over all ranks (the benchmark aborts when it is not small)."""
+    import torch
+    import torch.distributed as dist
+    import helix_a2a_b200 as helix
+    from helix_a2a_b200.ops import attention, reference_math as rm
+    cfg = stack.cfg
+    o, lse = attention.gqa_decode(q_layer0, stack.k_cache[0], stack.v_cache[0], stack.block_table, stack.seq_lens,
+                                  scale=stack.scale, max_seq_len=stack.local_ctx)
+    got = helix.alltoall_combine(o, lse, stack.workspace, rank, world)
+    B, H, D = o.shape
+    Hl = H // world
+    so = o.view(B, world, Hl, D).permute(1, 0, 2, 3).contiguous()
+    sl = lse.view(B, world, Hl).permute(1, 0, 2).contiguous()
+    ro, rl = torch.empty_like(so), torch.empty_like(sl)
+    dist.all_to_all_single(ro.view(-1), so.view(-1), group=group)
+    dist.all_to_all_single(rl.view(-1), sl.view(-1), group=group)
+    want = rm.lse_combine(ro, rl)
+    err = float((got.float() - want).abs().max())
+    if not (err == err):
+        err = float("inf")
+    return max_over_ranks(err, world)
+
+
 def run_helix(args):
     import torch
     if not args.no_pdl:
@@ -154,8 +217,15 @@ def run_helix(args):
         stack.decode_step_device(q_dev)
     barrier(world)
     check_compute_status(q_dev)
+    exchange_err = None
     if world > 1:
         helix.check_status(stack.workspace, rank, world)
+        # a wrong exchange must not print a tok/s line: compare one layer with the NCCL + torch path first
+        exchange_err = check_exchange_against_nccl(stack, q_dev[0], rank, world, group)
+        if not exchange_err < 2e-2:
+            if rank == 0:
+                print(f"bench: exchange + combine differs from the NCCL + torch path by {exchange_err}", file=sys.stderr)
+            raise SystemExit(1)
 
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
@@ -191,16 +261,8 @@ def run_helix(args):
     if world > 1:
         o = torch.randn(batch, cfg.n_q_heads, cfg.head_dim, device="cuda").bfloat16()
         lse = torch.randn(batch, cfg.n_q_heads, device="cuda")
-        for _ in range(20):
-            helix.alltoall_combine(o, lse, stack.workspace, rank, world)
-        barrier(world)
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a0.record()
-        for _ in range(200):
-            helix.alltoall_combine(o, lse, stack.workspace, rank, world)
-        a1.record()
-        barrier(world)
-        a2a_us = max_over_ranks(a0.elapsed_time(a1), world) / 200 * 1e3
+        a2a_us = time_op_in_graph(lambda: helix.alltoall_combine(o, lse, stack.workspace, rank, world), world)
+        helix.check_status(stack.workspace, rank, world)
 
     if rank == 0:
         kv_bytes = 2 * cfg.n_layers * batch * local_ctx * cfg.n_kv_heads * cfg.head_dim * 2
@@ -210,18 +272,24 @@ def run_helix(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init weights, KV ~ N(0,1), random q)",
             "impl": "helix_a2a_b200",
-            "config": {"model": f"llama3-70b-arch attention stack ({cfg.n_layers} layers, 64q/8kv heads, d=128, hidden 8192)",
-                       "global_batch": batch, "seq_len": args.ctx, "parallelism": f"cp{world}",
-                       "page_size": cfg.page_size, "kv_tokens_per_gpu_per_seq": local_ctx,
-                       "l2": "inputs larger than L2 (KV cache read per step: %.1f GB per GPU)" % (kv_bytes / 1e9),
-                       "cuda_graph": not args.no_graph, "one_kernel_exchange_oproj": world > 1 and args.fuse_oproj, "pdl": os.environ.get("HELIX_A2A_ENABLE_PDL", "0") == "1",
-                       "oproj_weights": "packed once at load time (tile-major, pre-swizzled bf16; same values)" if getattr(stack, "prepack_oproj", False) and not (world > 1 and args.fuse_oproj) else "plain [hidden, K]"},
+            "config": bench_config(cfg.n_layers, batch, args.ctx, world, cfg.page_size, local_ctx, kv_bytes,
+                                   not args.no_graph),
             "clocks": clocks,
             "e2e": {"value": batch / (ms_e2e * 1e-3), "unit": "tok/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": stack.h2d_bytes_per_step(), "d2h_bytes_per_step": stack.d2h_bytes_per_step()},
             "gpu_launches": stack.kernels_per_step() * args.steps,
-            "extras": {"helix_a2a_combine_us": a2a_us, "hbm_bytes_per_step_per_gpu": kv_bytes + w_bytes,
-                       "achieved_hbm_gbs": (kv_bytes + w_bytes) / (ms * 1e-3) / 1e9},
+            "extras": {"helix_a2a_combine_us": a2a_us, "helix_a2a_combine_us_how": "CUDA graph of 20 calls, replayed",
+                       "exchange_check_max_err_vs_nccl_torch": exchange_err,
+                       "hbm_bytes_per_step_per_gpu": kv_bytes + w_bytes,
+                       "achieved_hbm_gbs": (kv_bytes + w_bytes) / (ms * 1e-3) / 1e9,
+                       "path": {"attention": "helix gqa_decode (sm_100a, TMA + mbarrier)",
+                                "exchange": ("helix exchange+combine+o_proj in one kernel" if args.fuse_oproj
+                                             else "helix exchange+combine (one kernel)") if world > 1 else "none (cp=1)",
+                                "o_proj": "helix tcgen05 GEMM, weights " +
+                                          ("packed once at load time (tile-major, pre-swizzled bf16; same values)"
+                                           if getattr(stack, "prepack_oproj", False) and not (world > 1 and args.fuse_oproj)
+                                           else "plain [hidden, K]"),
+                                "pdl": os.environ.get("HELIX_A2A_ENABLE_PDL", "0") == "1"}},
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -88,7 +88,7 @@ def run_reference(args) -> None:
         import bench as _b  # noqa: F401
     except Exception as e:  # noqa: BLE001
         return _unavailable(f"import failed: {e!r}"[:200])
-    from bench import ClockSampler, METRIC, barrier, init_dist, max_over_ranks
+    from bench import ClockSampler, METRIC, barrier, bench_config, init_dist, max_over_ranks, time_op_in_graph
 
     try:
         rank, world, group, cpu_group = init_dist(args.gpus)
@@ -209,16 +209,11 @@ def run_reference(args) -> None:
     if world > 1:
         o = torch.randn(batch, Hq, D, device=dev).bfloat16()
         lse = torch.randn(batch, Hq, device=dev)
-        for _ in range(20):
-            hook.dcp_a2a_lse_reduce(o, lse, cp)
-        barrier(world)
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a0.record()
-        for _ in range(200):
-            hook.dcp_a2a_lse_reduce(o, lse, cp)
-        a1.record()
-        barrier(world)
-        a2a_us = max_over_ranks(a0.elapsed_time(a1), world) / 200 * 1e3
+        try:
+            a2a_us = time_op_in_graph(lambda: hook.dcp_a2a_lse_reduce(o, lse, cp), world)
+        except Exception:  # noqa: BLE001  (capture refused: leave the figure out rather than report host overhead)
+            a2a_us = None
+            torch.cuda.synchronize()
 
     if rank == 0:
         kv_bytes = 2 * L * batch * local_ctx * Hkv * D * 2
@@ -227,17 +222,16 @@ def run_reference(args) -> None:
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init weights, KV ~ N(0,1), random q)",
             "impl": "reference",
-            "config": {"model": f"llama3-70b-arch attention stack ({L} layers, 64q/8kv heads, d=128, hidden 8192)",
-                       "global_batch": batch, "seq_len": args.ctx, "parallelism": f"cp{world}", "page_size": page,
-                       "attention": att_name, "exchange": "reference helix_a2a.alltoall + its Triton combine"
-                       if world > 1 else "none (cp=1 passthrough in the reference's hook)",
-                       "o_proj": "torch.nn.functional.linear", "cuda_graph": graph is not None,
-                       "l2": "inputs larger than L2 (KV cache read per step: %.1f GB per GPU)" % (kv_bytes / 1e9)},
+            "config": bench_config(L, batch, args.ctx, world, page, local_ctx, kv_bytes, graph is not None),
             "clocks": clocks,
             "e2e": {"value": batch / (ms_e2e * 1e-3), "unit": "tok/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": L * batch * Hq * D * 2, "d2h_bytes_per_step": batch * hidden * 2},
             "gpu_launches": 0,
-            "extras": {"helix_a2a_combine_us": a2a_us},
+            "extras": {"helix_a2a_combine_us": a2a_us, "helix_a2a_combine_us_how": "CUDA graph of 20 calls, replayed",
+                       "path": {"attention": att_name,
+                                "exchange": "reference helix_a2a.alltoall + its Triton combine" if world > 1
+                                else "none (cp=1 passthrough in the reference's hook)",
+                                "o_proj": "torch.nn.functional.linear", "pdl": False}},
         }), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -36,10 +36,11 @@ struct GqaDecodeParams {
                                // static share, exit, end of the last drawn chunk, chunks drawn | pools visited << 32
   int B, Hq, Hkv, page_size, ctas;
   // Dynamic tail: of every pair with at least dyn_min_blocks KV blocks, the last dyn_pct percent (rounded down to
-  // whole chunks of dyn_chunk blocks) are not part of any CTA's fixed share; the warps of a CTA whose share is
-  // done draw them chunk by chunk, so SMs that stream faster end up streaming more.  dyn_pct = 0: fixed shares
-  // only.  max_helper: helper piece slots behind the 2 * ctas fixed ones (>= ctas * kGqaMaxVisits, or 0).
-  int dyn_pct, dyn_chunk, dyn_min_blocks, max_helper;
+  // whole chunks of dyn_chunk blocks) are not part of any CTA's fixed share; a CTA whose share is done draws
+  // them chunk by chunk, dyn_ahead chunks before its warps run out of blocks, so SMs that stream faster end up
+  // streaming more.  dyn_pct = 0: fixed shares only.  max_helper: helper piece slots behind the 2 * ctas fixed
+  // ones (>= ctas * kGqaMaxVisits, or 0).
+  int dyn_pct, dyn_chunk, dyn_ahead, dyn_min_blocks, max_helper;
   float scale;
   int lse_base2;
   // 1: the kernel before this one in the stream writes at most the newest token of each sequence (the cache
@@ -65,7 +66,8 @@ int gqa_pick_ctas(int B, int Hkv, int max_seq_len, int sm_count);
 
 // Dynamic-tail settings for a launch of `ctas` CTAs: fills dyn_pct / dyn_chunk / dyn_min_blocks / max_helper of *p
 // (pct_override / chunk_override < 0: the library's choice; max_helper 0 switches the dynamic tail off).
-void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int pct_override, int chunk_override);
+void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int pct_override, int chunk_override,
+                      int ahead_override);
 
 cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t stream);
 

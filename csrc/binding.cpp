@@ -9,6 +9,10 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <map>
+#include <memory>
+#include <mutex>
+
 #include <cstdlib>
 #include <limits>
 #include <string>
@@ -368,18 +372,35 @@ TORCH_LIBRARY(helix_a2a_b200, m) {
 // ---- pybind module: allocator + host utilities ---------------------------------------------------
 namespace py = pybind11;
 
+// Allocations are shared between the Python handle and every tensor made from them: the mappings go away when
+// the last of these is gone, so an alias of the workspace that outlives the handle object stays valid.
+static std::mutex g_vmm_mu;
+static std::map<uintptr_t, std::shared_ptr<helix::vmm::Allocation>> g_vmm;
+
+static uintptr_t vmm_register(helix::vmm::Allocation* a) {
+  std::lock_guard<std::mutex> lk(g_vmm_mu);
+  g_vmm[(uintptr_t)a] = std::shared_ptr<helix::vmm::Allocation>(a, [](helix::vmm::Allocation* p) { helix::vmm::destroy(p); });
+  return (uintptr_t)a;
+}
+
 static torch::Tensor vmm_as_tensor(uintptr_t handle, int64_t device) {
-  auto* a = reinterpret_cast<helix::vmm::Allocation*>(handle);
+  std::shared_ptr<helix::vmm::Allocation> owner;
+  {
+    std::lock_guard<std::mutex> lk(g_vmm_mu);
+    auto it = g_vmm.find(handle);
+    TORCH_CHECK(it != g_vmm.end(), "helix: unknown or closed workspace handle");
+    owner = it->second;
+  }
+  auto* a = owner.get();
   int64_t cp = helix::vmm::cp_size(a);
   int64_t elems = (int64_t)helix::vmm::mapped_row_bytes(a) / 8;
   int64_t stride = (int64_t)helix::vmm::row_stride(a) / 8;
   // Row 0 may be another GPU's memory, so the pointer's own device is not this rank's device:
   // name the target device explicitly instead of letting ATen query the pointer.
   auto opts = torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA);
-  // the Python side keeps the allocation alive for as long as the tensor exists
   return at::for_blob(reinterpret_cast<void*>(helix::vmm::base_address(a)), {cp, elems})
       .strides({stride, 1})
-      .deleter([](void*) {})
+      .deleter([owner](void*) mutable { owner.reset(); })     // the storage holds a share of the allocation
       .options(opts)
       .target_device(c10::Device(c10::kCUDA, (c10::DeviceIndex)device))
       .make_tensor();
@@ -388,10 +409,10 @@ static torch::Tensor vmm_as_tensor(uintptr_t handle, int64_t device) {
 PYBIND11_MODULE(_C, m) {
   m.doc() = "helix_a2a_b200 native module";
   m.def("vmm_create", [](int cp, int rank, int device, size_t row_bytes, int kind) {
-    return (uintptr_t)helix::vmm::create(cp, rank, device, row_bytes, (helix::vmm::HandleKind)kind);
+    return vmm_register(helix::vmm::create(cp, rank, device, row_bytes, (helix::vmm::HandleKind)kind));
   });
   m.def("vmm_create_single_process", [](std::vector<int> devices, size_t row_bytes) {
-    return (uintptr_t)helix::vmm::create_single_process(devices, row_bytes);
+    return vmm_register(helix::vmm::create_single_process(devices, row_bytes));
   });
   m.def("vmm_export_fd", [](uintptr_t h) { return helix::vmm::export_fd((helix::vmm::Allocation*)h); });
   m.def("vmm_export_fabric", [](uintptr_t h) { return py::bytes(helix::vmm::export_fabric((helix::vmm::Allocation*)h)); });
@@ -408,7 +429,17 @@ PYBIND11_MODULE(_C, m) {
   m.def("vmm_row_bytes", [](uintptr_t h) { return helix::vmm::mapped_row_bytes((helix::vmm::Allocation*)h); });
   m.def("vmm_base", [](uintptr_t h) { return helix::vmm::base_address((helix::vmm::Allocation*)h); });
   m.def("vmm_tensor", &vmm_as_tensor);
-  m.def("vmm_destroy", [](uintptr_t h) { helix::vmm::destroy((helix::vmm::Allocation*)h); });
+  // drops the handle's share; the rows are unmapped once no tensor made from the handle is alive either
+  m.def("vmm_destroy", [](uintptr_t h) {
+    std::shared_ptr<helix::vmm::Allocation> last;
+    {
+      std::lock_guard<std::mutex> lk(g_vmm_mu);
+      auto it = g_vmm.find(h);
+      if (it == g_vmm.end()) return;
+      last = std::move(it->second);
+      g_vmm.erase(it);
+    }
+  });
   m.def("close_fd", [](int fd) { return ::close(fd); });
 
   m.def("last_launch_info", []() {

@@ -173,7 +173,7 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   // HELIX_A2A_ATTN_DYN_PCT / HELIX_A2A_ATTN_DYN_CHUNK: share of every long pair that is handed out dynamically
   // (0 = fixed shares only) and the chunk size in 16-token blocks; unset = the library's choice
   helix::gqa_plan_dynamic(&p, (int)std::max<int64_t>(max_seq_len, 1), max_helper, env_int("HELIX_A2A_ATTN_DYN_PCT", -1),
-                          env_int("HELIX_A2A_ATTN_DYN_CHUNK", -1));
+                          env_int("HELIX_A2A_ATTN_DYN_CHUNK", -1), env_int("HELIX_A2A_ATTN_DYN_AHEAD", -1));
   if (const int mb = env_int("HELIX_A2A_ATTN_DYN_MIN_BLOCKS", -1); mb >= 0) p.dyn_min_blocks = mb;
   p.scale = (float)scale;
   p.lse_base2 = lse_base2 ? 1 : 0;

@@ -52,6 +52,7 @@ constexpr int kSmemPipe = kWarps * kStages * kStageBytes;   // 196608
 constexpr int kMergeBytes = kWarps * 4 * kD * 4;        // 16384: warps' partial O of four heads / piece list of a fold
 constexpr int kSmemBytes = kSmemPipe + kMergeBytes + 1024;   // + alignment slack
 constexpr int kMaxList = kMergeBytes / 4;               // pieces one fold can list
+constexpr int kQueue = 16;                              // drawn chunks a CTA can have published at a time
 static_assert(2 * kGqaMaxCtas <= kMaxList, "a fold lists at most one fixed piece and one helper piece per CTA");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -158,7 +159,10 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
   __shared__ float s_m[kWarps][8], s_l[kWarps][8];
   __shared__ int s_flag;                         // CTA-wide broadcast word (last arrival, scan result, list length)
   __shared__ int s_dynblk[2];                    // pool blocks the warps streamed in this segment (two slots, alternating)
-  __shared__ int s_cursor[2];                    // next block of the segment's fixed range to hand to a warp (alternating)
+  __shared__ int s_cursor[2];                    // next block of the segment's queue to hand to a warp (alternating)
+  __shared__ int s_chunk_base[kQueue];           // first KV block of a drawn chunk (-1: the pool was empty)
+  __shared__ int s_chunk_ready[kQueue];          // tag of the chunk whose base is valid in that slot
+  __shared__ int s_closed;                       // tag of the segment whose pool is known to be empty
   __shared__ int s_nb[kGqaSeqTable];             // KV blocks of each sequence
   __shared__ unsigned short s_nc[kGqaSeqTable];  // chunks in each of its pairs' pools
 
@@ -179,6 +183,8 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
     s_dynblk[1] = 0;
     s_cursor[0] = 0;
     s_cursor[1] = 0;
+    s_closed = 0;
+    for (int i = 0; i < kQueue; ++i) s_chunk_ready[i] = 0;
   }
   const bool early_kv = p.kv_stable != 0;
   if (!early_kv) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -322,48 +328,93 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
   };
 
   // ---- per-warp loader: which block comes next, and the loads in flight -------------------------------
-  int ld_mode = 2;           // 0: blocks of the fixed share, 1: chunks drawn from the pool, 2: nothing more
-  int ld_base = 0, ld_len = 0, ld_kvh = 0, ld_nc = 0, ld_ns = 0, ld_par = 0;
+  // The blocks of a segment form the CTA's queue: first the blocks of the fixed share, then the chunks drawn
+  // from the pair's pool.  Warps take one block at a time from a cursor in shared memory, so a warp that
+  // streams faster takes more.  The warp that takes queue position t0 + k * cd (t0 = `ahead` chunks before the
+  // end of what the queue holds) draws chunk k from the pool with a global atomic and publishes its first
+  // block a few blocks later, when the atomic's round trip (several microseconds under load) is over; so the
+  // queue is refilled `ahead` chunks before it runs dry and nobody waits for an atomic.
+  int ld_mode = 2;           // 0: taking blocks from the queue, 2: nothing more
+  int ld_base = 0, ld_len = 0, ld_kvh = 0, ld_nc = 0, ld_ns = 0, ld_par = 0, ld_t0 = 0, ld_tag = 0;
   bool ld_pool = false;
   const int32_t* ld_bt = p.block_table;
   int* ld_ctr = pool_ctr;
-  int ck_kb = 0, ck_left = 0, c_raw = 0;         // current chunk; the draw in flight lives in lane 0's c_raw
+  int c_raw = 0;                                 // lane 0: result of this warp's draw in flight
+  bool pd_valid = false;
+  int pd_k = 0, pd_age = 0;
   int pend_kb = 0, pend_page = 0;
   bool pend_valid = false;
   int issued = 0, consumed = 0, my_dyn = 0;
   int kq0 = 0, kq1 = 0, kq2 = 0;                 // block index of the load in each ring stage
+  const int ahead = max(p.dyn_ahead, 1);
 
+  auto publish_pending = [&]() {
+    if (!pd_valid) return;
+    const int c = __shfl_sync(0xffffffffu, c_raw, 0);          // waits for the atomic if it is still in flight
+    const int base_kb = c < ld_nc ? ld_ns + c * cd : -1;
+    if (lane == 0) {
+      s_chunk_base[pd_k % kQueue] = base_kb;
+      __threadfence_block();
+      *reinterpret_cast<volatile int*>(&s_chunk_ready[pd_k % kQueue]) = ld_tag + pd_k + 1;
+      if (base_kb < 0) *reinterpret_cast<volatile int*>(&s_closed) = ld_tag;
+    }
+    pd_valid = false;
+  };
+  auto issue_draw = [&](int k) {
+    publish_pending();                                         // one draw in flight per warp
+    ++n_drawn;
+    if (*reinterpret_cast<volatile int*>(&s_closed) == ld_tag) {
+      if (lane == 0) {                                         // the pool is known to be empty: no atomic needed
+        s_chunk_base[k % kQueue] = -1;
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&s_chunk_ready[k % kQueue]) = ld_tag + k + 1;
+      }
+      return;
+    }
+    if (lane == 0) c_raw = atomicAdd(ld_ctr, 1);
+    pd_valid = true;
+    pd_k = k;
+    pd_age = 0;
+  };
   auto gen_advance = [&]() {
     pend_valid = false;
     if (ld_mode == 0) {
       int i = 0;
       if (lane == 0) i = atomicAdd(&s_cursor[ld_par], 1);
       i = __shfl_sync(0xffffffffu, i, 0);
+      if (pd_valid && ++pd_age >= 3) publish_pending();
+      if (ld_pool) {
+        const int t = i - ld_t0;
+        if (t >= 0 && t % cd == 0) issue_draw(t / cd);
+      }
       if (i < ld_len) {
         pend_kb = ld_base + i;
         pend_valid = true;
+      } else if (!ld_pool) {
+        ld_mode = 2;
       } else {
-        ld_mode = ld_pool ? 1 : 2;
-        if (p.trace != nullptr && ld_pool && t_static == 0) t_static = now_ns();
-      }
-    }
-    if (!pend_valid && ld_mode == 1) {
-      if (ck_left == 0) {
-        const int c = __shfl_sync(0xffffffffu, c_raw, 0);
-        if (c < ld_nc) {
-          ck_kb = ld_ns + c * cd;
-          ck_left = cd;
-          ++n_drawn;
-          if (lane == 0) c_raw = atomicAdd(ld_ctr, 1);   // the next draw: its round trip hides behind this chunk
-        } else {
-          ld_mode = 2;
+        if (p.trace != nullptr && t_static == 0) t_static = now_ns();
+        const int j = (i - ld_len) / cd, off = (i - ld_len) % cd;
+        volatile int* rdy = reinterpret_cast<volatile int*>(&s_chunk_ready[j % kQueue]);
+        if (*rdy != ld_tag + j + 1) {
+          publish_pending();                 // never wait while holding a result that others may be waiting for
+          unsigned spins = 0;
+          while (*rdy != ld_tag + j + 1) {
+            if ((++spins & 255u) == 0u && now_ns() > deadline) {
+              ok = false;
+              break;
+            }
+          }
         }
-      }
-      if (ld_mode == 1) {
-        pend_kb = ck_kb++;
-        --ck_left;
-        ++my_dyn;
-        pend_valid = true;
+        const int base_kb = ok ? *reinterpret_cast<volatile int*>(&s_chunk_base[j % kQueue]) : -1;
+        if (base_kb < 0) {
+          ld_mode = 2;
+          publish_pending();                 // leaving: hand over what this warp still holds
+        } else {
+          pend_kb = base_kb + off;
+          ++my_dyn;
+          pend_valid = true;
+        }
       }
     }
     // the page id is looked up one block ahead of the copy that needs it, so the (dependent) block-table
@@ -394,19 +445,20 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
   auto seg_begin = [&](const Seg& sg) {
     ld_mode = 0;
     ld_par ^= 1;
+    ld_tag += 1 << 16;
     ld_base = sg.kb_begin;
     ld_len = sg.kb_end - sg.kb_begin;
     ld_kvh = sg.kvh;
     ld_pool = sg.pool;
     ld_nc = seq_nc(sg.b);
     ld_ns = sg.n_blocks - ld_nc * cd;
+    ld_t0 = ld_len - ahead * cd;
     ld_bt = p.block_table + (int64_t)sg.b * p.bt_stride;
     ld_ctr = pool_ctr + (sg.b * Hkv + sg.kvh);
-    ck_left = 0;
     issued = consumed = 0;
     my_dyn = 0;
-    c_raw = INT_MAX;
-    if (ld_pool && lane == 0) c_raw = atomicAdd(ld_ctr, 1);
+    // chunks whose drawing position lies before the start of the queue are drawn right away, one per warp
+    if (ld_pool && ld_t0 < 0 && warp < min((-ld_t0 + cd - 1) / cd, kWarps)) issue_draw(warp);
     gen_advance();
     while (issued < kStages && pend_valid) issue_pending();
   };
@@ -743,26 +795,30 @@ int gqa_pick_ctas(int B, int Hkv, int max_seq_len, int sm_count) {
   return (int)std::min<long long>(ctas, kGqaMaxCtas);
 }
 
-void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int pct_override, int chunk_override) {
+void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int pct_override, int chunk_override,
+                      int ahead_override) {
   const int nb = std::max(blocks_of(std::max(max_seq_len, 1)), 1);
   const long long blocks = (long long)std::max(p->B, 1) * p->Hkv * nb;
   p->max_helper = std::min(std::max(max_helper, 0), kGqaMaxHelper);
   p->dyn_min_blocks = 64;
-  // a dynamic tail only pays when a CTA's fixed share is long compared with a chunk
-  int pct = 0;   // fixed shares unless the caller asks otherwise
-  (void)blocks;
+  // a dynamic tail only pays when a CTA's fixed share is long compared with what it keeps drawn ahead
+  int pct = (blocks / std::max(p->ctas, 1) >= 256 && p->B <= kGqaSeqTable) ? 30 : 0;
   if (pct_override >= 0) pct = std::min(pct_override, 90);
-  int chunk = chunk_override > 0 ? chunk_override : 2;
+  const int chunk = chunk_override > 0 ? chunk_override : 8;
+  // a global atomic takes about 4 us when HBM is saturated, in which a CTA streams ~24 blocks: stay ~32 ahead
+  int ahead = ahead_override > 0 ? ahead_override : (32 + chunk - 1) / chunk;
+  ahead = std::min(std::max(ahead, 1), 8);
   if (p->max_helper < p->ctas * kGqaMaxVisits) pct = 0;    // every CTA needs its helper slots
   p->dyn_pct = pct;
   p->dyn_chunk = chunk;
+  p->dyn_ahead = ahead;
 }
 
 cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t stream) {
   if (p.B <= 0) return cudaSuccess;
   if (p.Hq % p.Hkv != 0 || p.Hq / p.Hkv > 8 || p.page_size % kBlockTok != 0 || p.ctas < 1 || p.ctas > kGqaMaxCtas ||
       p.max_helper < 0 || p.max_helper > kGqaMaxHelper || p.dyn_pct < 0 || p.dyn_pct > 90 ||
-      (p.dyn_pct > 0 && (p.dyn_chunk < 1 || p.max_helper < p.ctas * kGqaMaxVisits)))
+      (p.dyn_pct > 0 && (p.dyn_chunk < 1 || p.dyn_ahead < 1 || p.dyn_ahead > 8 || p.max_helper < p.ctas * kGqaMaxVisits)))
     return cudaErrorInvalidValue;
   static bool attr_set[64] = {false};
   int dev = 0;

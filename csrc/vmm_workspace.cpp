@@ -358,6 +358,10 @@ bool fabric_supported(int device) {
 
 void destroy(Allocation* a) {
   if (!a) return;
+  // Kernels of THIS process that still use the rows must be over before the mappings go away (a handle that is
+  // dropped while an exchange is in flight would otherwise unmap memory under it).  Peers that may still be
+  // storing into our row are the caller's business: barrier over the group before closing a workspace.
+  cudaDeviceSynchronize();
   for (int i = 0; i < a->cp; ++i) {
     if (a->mapped[i]) drv().MemUnmap(a->base + a->stride * i, a->row);
     if (a->handles[i]) drv().MemRelease(a->handles[i]);

@@ -14,7 +14,6 @@ reference this model runs inside vLLM (``benchmark/sbatch/run_gb200_aiperf_v3.sb
 from __future__ import annotations
 
 import math
-import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -63,7 +62,7 @@ class MlaDecodeStack:
         self.scales: List[torch.Tensor] = []
         self.kpe: List[torch.Tensor] = []
         self.w_o: List[torch.Tensor] = []
-        self.prepack_oproj = os.environ.get("HELIX_A2A_OPROJ_PREPACK", "1").strip() != "0"
+        self.prepack_oproj = env.oproj_prepack()
         self._w_o_packed = [None] * cfg.n_layers
         for _ in range(cfg.n_layers):
             # quantise in slabs to bound the fp32 temporaries

@@ -14,7 +14,6 @@ The reference leaves all of this to vLLM (``benchmark/sbatch/run_gb200_aiperf_v3
 from __future__ import annotations
 
 import math
-import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -23,6 +22,7 @@ import torch.distributed as dist
 
 from .. import api
 from ..ops import attention, oproj as oproj_mod
+from ..utils import env
 from ..utils.tracing import nvtx_range
 
 
@@ -73,7 +73,7 @@ class HelixDecodeStack:
         self.k_cache: List[torch.Tensor] = []
         self.v_cache: List[torch.Tensor] = []
         self.w_o: List[torch.Tensor] = []
-        self.prepack_oproj = os.environ.get("HELIX_A2A_OPROJ_PREPACK", "1").strip() != "0"
+        self.prepack_oproj = env.oproj_prepack()
         self._w_o_packed = [None] * cfg.n_layers
         for _ in range(cfg.n_layers):
             k = torch.empty(shape, dtype=cfg.dtype, device=self.device).normal_(0, kv_std, generator=gen)

@@ -88,7 +88,9 @@ def should_use_mnnvl(cpu_group, mnnvl_param="auto") -> bool:
 
 
 class VmmWorkspaceHandle:
-    """Owns a VMM allocation; destroying it unmaps all rows and releases the handles."""
+    """The Python-side share of a VMM allocation.  The rows stay mapped until this handle is closed AND every
+    tensor made from it is gone (the tensors' storages hold shares too); unmapping synchronises the device first.
+    Peers may still be storing into this rank's row: barrier over the group before closing a workspace."""
 
     def __init__(self, handle: int, kind: str, transport: str):
         self._h = handle

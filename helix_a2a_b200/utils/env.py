@@ -2,9 +2,12 @@
 
 The first four keep the names and meanings the reference uses
 (``csrc/helix_alltoall.cu:541-548``, ``csrc/torch_binding.cpp:25-32``,
-``helix_a2a/mnnvl.py:577-607``, ``patches/dcp_alltoall_helix.py:40``); the rest
-are new.  Unlike the reference, values are read on every call (cheap) so tests
-can flip them without re-importing.
+``helix_a2a/mnnvl.py:577-607``, ``patches/dcp_alltoall_helix.py:40``); the rest are new.  Unlike the
+reference, values are read on every call (cheap) so tests can flip them without re-importing.
+
+The functions below are the knobs that Python code reads; every Python reader goes through them.
+``EXTENSION_KNOBS`` lists the ones the native extension reads itself with ``getenv`` (on every call of
+the op concerned); they are here so that one place names every knob.
 """
 from __future__ import annotations
 
@@ -12,6 +15,21 @@ import os
 
 _TRUE = ("1", "true", "yes", "on")
 _FALSE = ("0", "false", "no", "off")
+
+#: knob -> (default, meaning); read by the C++ bindings (``csrc/binding.cpp``, ``csrc/binding_ops.cpp``)
+EXTENSION_KNOBS = {
+    "HELIX_A2A_ENABLE_PDL": ("0", "1: every kernel is launched with programmatic stream serialization"),
+    "HELIX_A2A_CHANNEL_COUNT": ("0", "0 / unset: the auto-tuner picks the exchange's channel count; n: exactly n"),
+    "HELIX_A2A_TIMEOUT_MS": ("2000", "time limit of every device-side wait of a call that does not pass its own"),
+    "HELIX_A2A_DEBUG": ("0", "1: exchange outputs are pre-filled with NaN so that an unwritten row shows"),
+    "HELIX_A2A_OPROJ_STREAMK": ("unset", "1 / 0: force / forbid the stream-K o_proj kernel where the library would choose"),
+    "HELIX_A2A_OPROJ_TRACE": ("0", "1: the stream-K o_proj kernel records %globaltimer stamps per CTA"),
+    "HELIX_A2A_ATTN_TRACE": ("0", "1: the GQA decode kernel records per-CTA %globaltimer stamps, SM id and chunk counts"),
+    "HELIX_A2A_ATTN_DYN_PCT": ("unset", "percent of every long (sequence, kv head) pair handed out dynamically; 0: fixed shares"),
+    "HELIX_A2A_ATTN_DYN_CHUNK": ("unset", "blocks of 16 tokens per dynamically drawn chunk"),
+    "HELIX_A2A_MLA_VARIANT": ("ws", "ws: producer + math warps; lockstep: all warps walk a tile's phases together"),
+    "HELIX_A2A_MLA_PROF": ("0", "1: the lockstep MLA kernel sums clock64 per phase of its tile loop"),
+}
 
 
 def enable_pdl() -> bool:
@@ -51,6 +69,20 @@ def timeout_ms() -> int:
         return 2000
 
 
+def hook_timeout_ms() -> int:
+    """``HELIX_A2A_HOOK_TIMEOUT_MS``: time limit of the waits of calls made through the vLLM hook (default 30 s:
+    ranks of a serving engine can be far apart during warm-up)."""
+    try:
+        return max(int(os.environ.get("HELIX_A2A_HOOK_TIMEOUT_MS", "30000")), 1)
+    except ValueError:
+        return 30000
+
+
+def hook_check() -> bool:
+    """``HELIX_A2A_HOOK_CHECK=0``: the import hook does not read the exchange's status after every engine step."""
+    return os.environ.get("HELIX_A2A_HOOK_CHECK", "1").strip() != "0"
+
+
 def handle_transport() -> str:
     """``HELIX_A2A_HANDLE_TRANSPORT``: ``auto`` | ``pidfd`` | ``scm`` | ``fabric`` - how the VMM handles of the
     workspace rows travel between ranks (POSIX fd duplicated with ``pidfd_getfd``, POSIX fd sent over a Unix
@@ -63,47 +95,14 @@ def handle_transport() -> str:
 
 
 def debug() -> bool:
+    """``HELIX_A2A_DEBUG=1``: NaN-poisoned outputs plus a check that every row was written."""
     return os.environ.get("HELIX_A2A_DEBUG", "0").strip() in _TRUE
-
-
-def oproj_streamk() -> str:
-    """``HELIX_A2A_OPROJ_STREAMK``: ``1`` / ``0`` forces / forbids the stream-K o_proj kernel for calls
-    that leave the choice to the library; unset = the library's heuristic.  Read by the extension."""
-    return os.environ.get("HELIX_A2A_OPROJ_STREAMK", "auto").strip().lower()
-
-
-def oproj_trace() -> bool:
-    """``HELIX_A2A_OPROJ_TRACE=1``: the stream-K o_proj kernel records ``%globaltimer`` stamps per CTA."""
-    return os.environ.get("HELIX_A2A_OPROJ_TRACE", "0").strip() == "1"
 
 
 def nccl_impl() -> str:
     """``HELIX_A2A_NCCL_IMPL``: what ``HELIX_A2A_BACKEND=nccl`` runs inside the vLLM hook - ``own``
-    (default: two ``all_to_all_single`` + torch combine) or ``stock`` (the replaced vLLM function)."""
+    (default: two ``all_to_all_single`` + the combine kernel) or ``stock`` (the replaced vLLM function)."""
     return os.environ.get("HELIX_A2A_NCCL_IMPL", "own").strip().lower()
-
-
-def vllm_hook_enabled() -> bool:
-    """``HELIX_A2A_VLLM_HOOK=0`` keeps the start-up shim (``vllm_patch/autoload``) from installing the import hook."""
-    return os.environ.get("HELIX_A2A_VLLM_HOOK", "1").strip() != "0"
-
-
-def mla_variant() -> str:
-    """``HELIX_A2A_MLA_VARIANT``: ``ws`` (default: producer warps + math warps) or ``lockstep`` (all warps
-    walk the phases of a tile together; the only one with the ``HELIX_A2A_MLA_PROF=1`` cycle profile)."""
-    return os.environ.get("HELIX_A2A_MLA_VARIANT", "ws").strip().lower()
-
-
-def attn_trace() -> bool:
-    """``HELIX_A2A_ATTN_TRACE=1``: the GQA decode attention kernel records four ``%globaltimer`` stamps per
-    CTA (entry, first data, end of streaming, exit; the SM id rides in the low byte of the second)."""
-    return os.environ.get("HELIX_A2A_ATTN_TRACE", "0").strip() == "1"
-
-
-def mla_prof() -> bool:
-    """``HELIX_A2A_MLA_PROF=1``: the lockstep MLA kernel sums ``clock64`` per phase of its tile loop
-    (read back with ``ops().attn_trace``)."""
-    return os.environ.get("HELIX_A2A_MLA_PROF", "0").strip() == "1"
 
 
 def nvtx() -> bool:

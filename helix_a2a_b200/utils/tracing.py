@@ -9,13 +9,14 @@ synchronisation, that every row was written.  The reference has neither
 from __future__ import annotations
 
 import contextlib
-import os
 
 import torch
 
+from . import env
+
 
 def nvtx_enabled() -> bool:
-    return os.environ.get("HELIX_A2A_NVTX", "0") == "1" and torch.cuda.is_available()
+    return env.nvtx() and torch.cuda.is_available()
 
 
 @contextlib.contextmanager
@@ -31,7 +32,7 @@ def nvtx_range(name: str):
 
 
 def debug_enabled() -> bool:
-    return os.environ.get("HELIX_A2A_DEBUG", "0") == "1"
+    return env.debug()
 
 
 def check_written(t: torch.Tensor, what: str) -> None:

@@ -36,14 +36,15 @@ import torch.distributed as dist
 
 import helix_a2a_b200 as _helix
 from helix_a2a_b200.ops import reference_math as _rm
+from helix_a2a_b200.utils import env as _env
 
 logger = logging.getLogger(__name__)
 
-_HELIX_BACKEND = os.environ.get("HELIX_A2A_BACKEND", "nccl").lower()
+_HELIX_BACKEND = _env.backend()
 # What "nccl" means: "own" = two all_to_all_single + a torch combine, as in the reference's hook
 # (patches/dcp_alltoall_helix.py:455-504); "stock" = the function of the vLLM module this hook replaced.
-_NCCL_IMPL = os.environ.get("HELIX_A2A_NCCL_IMPL", "own").lower()
-_HOOK_TIMEOUT_MS = max(int(os.environ.get("HELIX_A2A_HOOK_TIMEOUT_MS", "30000") or 30000), 1)
+_NCCL_IMPL = _env.nccl_impl()
+_HOOK_TIMEOUT_MS = _env.hook_timeout_ms()
 _workspace: Optional[torch.Tensor] = None
 _workspace_key = None
 _stock_reduce = None     # vLLM's original function, when it could be imported
@@ -81,12 +82,8 @@ def dcp_a2a_check_status(raise_on_error: bool = True) -> dict:
 
 
 def _mnnvl_setting():
-    v = os.environ.get("HELIX_A2A_USE_MNNVL", "auto").strip().lower()
-    if v in ("0", "false", "no", "off"):
-        return False
-    if v in ("1", "true", "yes", "on"):
-        return True
-    return "auto"
+    v = _env.use_mnnvl()
+    return False if v == "0" else True if v == "1" else "auto"
 
 
 def _init_workspace(cp_rank: int, cp_size: int, cp_group, device: torch.device):
