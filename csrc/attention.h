@@ -29,18 +29,16 @@ struct GqaDecodeParams {
   //   [0, P)          blocks of each (sequence, kv head) pair that have been folded into a piece so far
   //   [P, 2P)         chunks drawn from each pair's dynamic pool          (touched only when dyn_pct > 0)
   //   [2P]            CTAs that have left the launch                      (touched only when dyn_pct > 0)
-  //   [2P + 8, ...)   per helper slot (kGqaMaxVisits per CTA): pair + 1 of the piece parked there
+  //   [2P + 8, ...)   one flag per helper slot: a piece has been parked there
   int* counters;
   int* error_flag;             // set to a helix::Status code when a bounded wait runs out
-  unsigned long long* trace;   // optional [ctas][8] stamps (%globaltimer): entry, first data | SM id, end of the
-                               // static share, exit, end of the last drawn chunk, chunks drawn | pools visited << 32
+  unsigned long long* trace;   // optional [ctas][8] stamps (%globaltimer): entry, first data, end of the fixed share,
+                               // exit, end of the last drawn chunk, chunks drawn | pools visited << 32, SM id
   int B, Hq, Hkv, page_size, ctas;
   // Dynamic tail: of every pair with at least dyn_min_blocks KV blocks, the last dyn_pct percent (rounded down to
-  // whole chunks of dyn_chunk blocks) are not part of any CTA's fixed share; a CTA whose share is done draws
-  // them chunk by chunk, dyn_ahead chunks before its warps run out of blocks, so SMs that stream faster end up
-  // streaming more.  dyn_pct = 0: fixed shares only.  max_helper: helper piece slots behind the 2 * ctas fixed
-  // ones (>= ctas * kGqaMaxVisits, or 0).
-  int dyn_pct, dyn_chunk, dyn_ahead, dyn_min_blocks, max_helper;
+  // whole chunks of dyn_chunk blocks) are not part of any CTA's fixed share; CTAs draw them chunk by chunk when
+  // their own share is done, so SMs that stream faster end up streaming more.  dyn_pct = 0: fixed shares only.
+  int dyn_pct, dyn_chunk, dyn_min_blocks, max_helper;
   float scale;
   int lse_base2;
   // 1: the kernel before this one in the stream writes at most the newest token of each sequence (the cache
@@ -52,8 +50,7 @@ struct GqaDecodeParams {
 };
 
 constexpr int kGqaMaxCtas = 640;     // upper bound of the grid
-constexpr int kGqaMaxVisits = 4;     // pools of other pairs one CTA may help with (one parked piece each)
-constexpr int kGqaMaxHelper = kGqaMaxCtas * kGqaMaxVisits;   // helper piece slots
+constexpr int kGqaMaxHelper = 1024;  // upper bound of the chunks all dynamic pools hold together
 constexpr int kGqaSeqTable = 256;    // batches beyond this run with fixed shares only
 
 // scratch sizes
@@ -66,8 +63,7 @@ int gqa_pick_ctas(int B, int Hkv, int max_seq_len, int sm_count);
 
 // Dynamic-tail settings for a launch of `ctas` CTAs: fills dyn_pct / dyn_chunk / dyn_min_blocks / max_helper of *p
 // (pct_override / chunk_override < 0: the library's choice; max_helper 0 switches the dynamic tail off).
-void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int pct_override, int chunk_override,
-                      int ahead_override);
+void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int pct_override, int chunk_override);
 
 cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t stream);
 

@@ -147,9 +147,7 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   torch::Tensor o = torch::empty({B, Hq, 128}, q.options());
   torch::Tensor lse = torch::empty({B, Hq}, q.options().dtype(torch::kFloat32));
   if (B == 0) return std::make_tuple(o, lse);
-  TORCH_CHECK((int64_t)B * Hkv * ((std::max<int64_t>(max_seq_len, 1) + 15) / 16 + 1) < (int64_t(1) << 31),
-              "B * Hkv * KV blocks must fit 31 bits");
-  const int max_helper = sp * helix::kGqaMaxVisits;
+  const int max_helper = helix::kGqaMaxHelper;
   // the o_proj counters sit in the last hidden / 128 ints of the same tensor: leave them room
   Scratch& sc = scratch_for(q.device(), (int64_t)helix::gqa_counter_ints(B * Hkv, max_helper) + 2048,
                             (int64_t)helix::gqa_part_o_floats(sp, max_helper),
@@ -173,7 +171,7 @@ std::tuple<torch::Tensor, torch::Tensor> gqa_decode(torch::Tensor q, torch::Tens
   // HELIX_A2A_ATTN_DYN_PCT / HELIX_A2A_ATTN_DYN_CHUNK: share of every long pair that is handed out dynamically
   // (0 = fixed shares only) and the chunk size in 16-token blocks; unset = the library's choice
   helix::gqa_plan_dynamic(&p, (int)std::max<int64_t>(max_seq_len, 1), max_helper, env_int("HELIX_A2A_ATTN_DYN_PCT", -1),
-                          env_int("HELIX_A2A_ATTN_DYN_CHUNK", -1), env_int("HELIX_A2A_ATTN_DYN_AHEAD", -1));
+                          env_int("HELIX_A2A_ATTN_DYN_CHUNK", -1));
   if (const int mb = env_int("HELIX_A2A_ATTN_DYN_MIN_BLOCKS", -1); mb >= 0) p.dyn_min_blocks = mb;
   p.scale = (float)scale;
   p.lse_base2 = lse_base2 ? 1 : 0;

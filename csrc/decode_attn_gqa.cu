@@ -43,17 +43,18 @@ using namespace sm100;
 
 constexpr int kD = 128;           // head dim
 constexpr int kBlockTok = 16;     // tokens per KV block (one MMA k-step of P V)
-constexpr int kWarps = 8;
+constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 3;
 constexpr int kTileBytes = kBlockTok * kD * 2;        // 4096: one K (or V) block
 constexpr int kStageBytes = 2 * kTileBytes;           // K + V
-constexpr int kSmemPipe = kWarps * kStages * kStageBytes;   // 196608
-constexpr int kMergeBytes = kWarps * 4 * kD * 4;        // 16384: warps' partial O of four heads / piece list of a fold
+constexpr int kSmemPipe = kWarps * kStages * kStageBytes;   // 98304
+constexpr int kMergeBytes = kWarps * 4 * kD * 4;        // 8192: warps' partial O of four heads / piece list of a fold
 constexpr int kSmemBytes = kSmemPipe + kMergeBytes + 1024;   // + alignment slack
 constexpr int kMaxList = kMergeBytes / 4;               // pieces one fold can list
-constexpr int kQueue = 16;                              // drawn chunks a CTA can have published at a time
-static_assert(2 * kGqaMaxCtas <= kMaxList, "a fold lists at most one fixed piece and one helper piece per CTA");
+constexpr int kMaxPoolChunks = kMaxList - kGqaMaxCtas;   // chunks one pair's pool may hold: a fold lists at most one piece
+                                                        // per CTA plus one per chunk of the pair
+static_assert(kMaxPoolChunks > 0, "the piece list must hold one piece per CTA");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -88,9 +89,9 @@ __device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
 }
 
 // The CTA whose piece completed a pair folds all pieces listed in s_list (piece slots) into the final output.
-// Warp w folds head w: lanes first share out the pieces' weights, then every lane sums four columns with
-// sixteen independent 16-byte loads in flight.  Kept out of line so that its registers do not weigh on the
-// streaming loop.
+// Warp w folds heads 2w and 2w + 1 together: lanes first share out the pieces' weights, then every lane sums
+// four columns of both heads with sixteen independent 16-byte loads in flight.  Kept out of line so that its
+// registers do not weigh on the streaming loop.
 struct FoldArgs {
   const float* part_o;
   const float* part_lse;
@@ -98,73 +99,105 @@ struct FoldArgs {
   float* lse;
   int Hq, lse_base2;
 };
+constexpr int kFoldBatch = 8;
 __device__ __noinline__ void fold_pieces(FoldArgs p, const int* s_list, int n_pieces, int st_b, int st_kvh, int group,
                                          int warp, int lane) {
-  for (int hg = warp; hg < group; hg += kWarps) {
-    float M = -INFINITY;
-    for (int i = lane; i < n_pieces; i += 32) M = fmaxf(M, __ldcg(p.part_lse + (size_t)s_list[i] * 8 + hg));
+  // Warp w folds heads 2w and 2w + 1.  Pieces are taken eight at a time: their LSEs and their rows are requested
+  // together (16 + 2 independent loads per lane), so a batch costs ONE round trip to L2; the running maximum is
+  // carried from batch to batch as in an online softmax.  (Sixteen at a time needs so many registers that the
+  // streaming loop of the kernel around this function starts to spill: measured 30 % slower.)
+  const int h0 = warp * 2, h1 = warp * 2 + 1;
+  if (h0 >= group) return;
+  const bool has1 = h1 < group;
+  float M0 = -INFINITY, M1 = -INFINITY, L0 = 0.f, L1 = 0.f;
+  float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = 0; c0 < n_pieces; c0 += kFoldBatch) {
+    const int nb = min(kFoldBatch, n_pieces - c0);
+    const int my_slot = lane < nb ? s_list[c0 + lane] : 0;
+    float l0 = -INFINITY, l1 = -INFINITY;
+    if (lane < nb) {
+      l0 = __ldcg(p.part_lse + (size_t)my_slot * 8 + h0);
+      if (has1) l1 = __ldcg(p.part_lse + (size_t)my_slot * 8 + h1);
+    }
+    float4 v0[kFoldBatch], v1[kFoldBatch];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    float L = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int c0 = 0; c0 < n_pieces; c0 += 32) {
-      const int i = c0 + lane;
-      float w = 0.f;
-      int my_slot = 0;
-      if (i < n_pieces) {
-        my_slot = s_list[i];
-        if (M != -INFINITY) w = fast_exp2(__ldcg(p.part_lse + (size_t)my_slot * 8 + hg) - M);
+    for (int j = 0; j < kFoldBatch; ++j) {
+      if (j < nb) {
+        const int sl = __shfl_sync(0xffffffffu, my_slot, j);
+        const float4* po = reinterpret_cast<const float4*>(p.part_o + (size_t)sl * 8 * kD);
+        v0[j] = __ldcg(po + h0 * (kD / 4) + lane);
+        if (has1) v1[j] = __ldcg(po + h1 * (kD / 4) + lane);
       }
-      L += w;
-      const int nbatch = min(32, n_pieces - c0);
-      for (int j0 = 0; j0 < nbatch; j0 += 16) {
-        float4 v[16];
+    }
+    float b0 = l0, b1 = l1;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (j0 + j < nbatch) {
-            const int sl = __shfl_sync(0xffffffffu, my_slot, j0 + j);
-            v[j] = __ldcg(reinterpret_cast<const float4*>(p.part_o + ((size_t)sl * 8 + hg) * kD) + lane);
-          }
-        }
+    for (int o = 16; o > 0; o >>= 1) {       // lanes beyond the batch hold -inf
+      b0 = fmaxf(b0, __shfl_xor_sync(0xffffffffu, b0, o));
+      b1 = fmaxf(b1, __shfl_xor_sync(0xffffffffu, b1, o));
+    }
+    const float n0 = fmaxf(M0, b0), n1 = fmaxf(M1, b1);
+    const float s0 = (M0 == -INFINITY) ? 0.f : fast_exp2(M0 - n0);
+    const float s1 = (M1 == -INFINITY) ? 0.f : fast_exp2(M1 - n1);
+    const float w0 = (l0 == -INFINITY) ? 0.f : fast_exp2(l0 - n0);
+    const float w1 = (l1 == -INFINITY) ? 0.f : fast_exp2(l1 - n1);
+    M0 = n0;
+    M1 = n1;
+    L0 = L0 * s0 + w0;
+    L1 = L1 * s1 + w1;
+    a0.x *= s0; a0.y *= s0; a0.z *= s0; a0.w *= s0;
+    a1.x *= s1; a1.y *= s1; a1.z *= s1; a1.w *= s1;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (j0 + j < nbatch) {
-            const float x = __shfl_sync(0xffffffffu, w, j0 + j);
-            acc.x += x * v[j].x;
-            acc.y += x * v[j].y;
-            acc.z += x * v[j].z;
-            acc.w += x * v[j].w;
-          }
+    for (int j = 0; j < kFoldBatch; ++j) {
+      if (j < nb) {
+        const float x0 = __shfl_sync(0xffffffffu, w0, j);
+        const float x1 = __shfl_sync(0xffffffffu, w1, j);
+        a0.x += x0 * v0[j].x;
+        a0.y += x0 * v0[j].y;
+        a0.z += x0 * v0[j].z;
+        a0.w += x0 * v0[j].w;
+        if (has1) {
+          a1.x += x1 * v1[j].x;
+          a1.y += x1 * v1[j].y;
+          a1.z += x1 * v1[j].z;
+          a1.w += x1 * v1[j].w;
         }
       }
     }
+  }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+  for (int o = 16; o > 0; o >>= 1) {
+    L0 += __shfl_xor_sync(0xffffffffu, L0, o);
+    L1 += __shfl_xor_sync(0xffffffffu, L1, o);
+  }
+  auto store_head = [&](int hg, float M, float L, const float4& a) {
     const float inv = L > 0.f ? 1.f / L : 0.f;
     const int h = st_kvh * group + hg;
     uint2 packed;
-    packed.x = pack_bf16(acc.x * inv, acc.y * inv);
-    packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+    packed.x = pack_bf16(a.x * inv, a.y * inv);
+    packed.y = pack_bf16(a.z * inv, a.w * inv);
     *reinterpret_cast<uint2*>(p.o + ((int64_t)st_b * p.Hq + h) * kD + lane * 4) = packed;
     if (lane == 0) {
       const float lse2 = L > 0.f ? M + log2f(L) : -INFINITY;
       p.lse[(int64_t)st_b * p.Hq + h] = p.lse_base2 ? lse2 : lse2 * kLn2;
     }
-  }
+  };
+  store_head(h0, M0, L0, a0);
+  if (has1) store_head(h1, M1, L1, a1);
 }
 
-__global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_constant__ GqaDecodeParams p) {
+// kTrace: the instance that records time stamps (the stamps cost registers the streaming loop needs)
+template <bool kTrace>
+__global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_constant__ GqaDecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kWarps][kStages];
   __shared__ float s_m[kWarps][8], s_l[kWarps][8];
   __shared__ int s_flag;                         // CTA-wide broadcast word (last arrival, scan result, list length)
-  __shared__ int s_dynblk[2];                    // pool blocks the warps streamed in this segment (two slots, alternating)
-  __shared__ int s_cursor[2];                    // next block of the segment's queue to hand to a warp (alternating)
-  __shared__ int s_chunk_base[kQueue];           // first KV block of a drawn chunk (-1: the pool was empty)
-  __shared__ int s_chunk_ready[kQueue];          // tag of the chunk whose base is valid in that slot
-  __shared__ int s_closed;                       // tag of the segment whose pool is known to be empty
+  __shared__ int s_draw[2];                      // chunk drawn ahead by thread 0 (two slots, used alternately)
+  __shared__ int s_scan;                         // chunk drawn while probing the other pools
   __shared__ int s_nb[kGqaSeqTable];             // KV blocks of each sequence
-  __shared__ unsigned short s_nc[kGqaSeqTable];  // chunks in each of its pairs' pools
+  __shared__ unsigned short s_nc[kGqaSeqTable];  // chunks a pair of the sequence would give to its pool ...
+  __shared__ unsigned short s_ncf[kGqaSeqTable]; // ... and what it does give, after the rules below
+  __shared__ int s_hb[kGqaSeqTable];             // first helper slot of the sequence's pools
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -179,92 +212,96 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
     mbar_fence_init();
     tma_prefetch_desc(&p.k_map);
     tma_prefetch_desc(&p.v_map);
-    s_dynblk[0] = 0;
-    s_dynblk[1] = 0;
-    s_cursor[0] = 0;
-    s_cursor[1] = 0;
-    s_closed = 0;
-    for (int i = 0; i < kQueue; ++i) s_chunk_ready[i] = 0;
   }
   const bool early_kv = p.kv_stable != 0;
   if (!early_kv) asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const unsigned long long t_entry = now_ns();
   const unsigned long long deadline = t_entry + p.timeout_ns;
-  unsigned long long t_static = 0, t_dyn = 0;
+  unsigned long long t_first = 0, t_static = 0, t_dyn = 0;
   unsigned n_drawn = 0, n_visits = 0;
 
   // ---- per-sequence tables and totals ------------------------------------------------------------
   const int cd = p.dyn_chunk;
-  const bool dyn_on = p.dyn_pct > 0 && cd > 0 && p.B <= kGqaSeqTable && p.max_helper > 0;
+  const bool dyn_cfg = p.dyn_pct > 0 && cd > 0 && p.B <= kGqaSeqTable && p.max_helper > 0;
+  bool dyn_on = false;                           // some pair of this launch really has a pool
   const int n_tab = min(p.B, kGqaSeqTable);
-  for (int i = tid; i < n_tab; i += kThreads) s_nb[i] = blocks_of(p.seq_lens[i]);
+  for (int i = tid; i < n_tab; i += kThreads) {
+    // (the divisions are done here, one sequence per thread, not in the serial pass below)
+    const int nb = blocks_of(p.seq_lens[i]);
+    s_nb[i] = nb;
+    s_nc[i] = (unsigned short)min(dyn_cfg ? dyn_chunks_of(nb, p.dyn_pct, cd, p.dyn_min_blocks) : 0, 65535);
+  }
   __syncthreads();
-  int total_s = 0;                               // blocks in the fixed shares (the host checked that this fits an int)
+  long long total_s = 0;                         // blocks in the fixed shares
   {
     long long total = 0;
     for (int b = 0; b < n_tab; ++b) total += s_nb[b];
     for (int b = kGqaSeqTable; b < p.B; ++b) total += blocks_of(p.seq_lens[b]);
-    // A pair only gets a pool if what stays in the fixed shares is longer than any share.  A CTA's share then
+    // A pair only gets a pool if what stays in the fixed shares is longer than two shares.  A CTA's share then
     // never holds such a pair from its first block to its last fixed block, so the share's two piece slots
-    // (one for a pair it continues, one for a pair it starts) still suffice; and some share ends inside the
-    // pair, so the pair has at least one CTA that stays on its pool until the pool is empty.
-    const long long share_max = (total * Hkv + G - 1) / G;
+    // (one for a pair it continues, one for a pair it starts) still suffice; some share ends inside the pair, so
+    // a CTA is there to take up the pool; and pairs of about a share's length, where nearly every chunk would end
+    // up as a parked piece of its own, keep their fixed shares only (measured slower with pools).
+    const long long share_max = 2 * ((total * Hkv + G - 1) / G);
+    int hb = 0;
     for (int b = 0; b < n_tab; ++b) {
       const int nb = s_nb[b];
-      int nc = dyn_on ? dyn_chunks_of(nb, p.dyn_pct, cd, p.dyn_min_blocks) : 0;
-      if (nb - nc * cd <= share_max || nc > 65535) nc = 0;
-      if (tid == 0) s_nc[b] = (unsigned short)nc;
+      int nc = s_nc[b];
+      if (nb - nc * cd <= share_max) nc = 0;
+      if (hb + nc * Hkv > p.max_helper || nc > kMaxPoolChunks) nc = 0;    // never more chunks than helper slots
+      if (tid == 0) {
+        s_ncf[b] = (unsigned short)nc;
+        s_hb[b] = hb;
+      }
+      hb += nc * Hkv;
       total_s += nb - nc * cd;
     }
     for (int b = kGqaSeqTable; b < p.B; ++b) total_s += blocks_of(p.seq_lens[b]);
     total_s *= Hkv;
+    dyn_on = hb > 0;
   }
   __syncthreads();
   auto seq_nb = [&](int b) { return b < kGqaSeqTable ? s_nb[b] : blocks_of(p.seq_lens[b]); };
-  auto seq_nc = [&](int b) { return (dyn_on && b < kGqaSeqTable) ? (int)s_nc[b] : 0; };
+  auto seq_nc = [&](int b) { return (dyn_on && b < kGqaSeqTable) ? (int)s_ncf[b] : 0; };
   auto seq_ns = [&](int b) { return seq_nb(b) - seq_nc(b) * cd; };
 
-  const int share = max((total_s + G - 1) / G, 1);
-  const int g0 = (int)min((long long)blockIdx.x * share, (long long)total_s);
-  const int g1 = min(total_s, g0 + share);
+  const long long share = max((total_s + G - 1) / (long long)G, 1LL);
+  const long long g0 = (long long)blockIdx.x * share;
+  const long long g1 = min(total_s, g0 + share);
 
+  int* const done_ctr = p.counters;                      // [P]
+  int* const pool_ctr = p.counters + (size_t)p.B * Hkv;   // [P]
+  int* const exit_ctr = p.counters + (size_t)2 * p.B * Hkv;
+  int* const helper_flag = exit_ctr + 8;                 // [max_helper]
   const int P = p.B * Hkv;
-  int* const done_ctr = p.counters;              // [P]
-  int* const pool_ctr = p.counters + P;          // [P]
-  int* const exit_ctr = p.counters + 2 * P;
-  int* const helper_pair = exit_ctr + 8;         // [max_helper]: pair + 1 of the piece parked in each helper slot
 
   uint8_t* my_smem = smem + warp * (kStages * kStageBytes);
   const float sl2 = p.scale * kLog2e;
   const int mi = lane >> 3, r8 = lane & 7;
   const uint32_t k_row = (uint32_t)(((mi >> 1) << 3) + r8), k_csel = (uint32_t)(mi & 1);
   const uint32_t v_row = (uint32_t)(((mi & 1) << 3) + r8), v_csel = (uint32_t)(mi >> 1);
-  int it_ring = 0;           // TMA iterations consumed so far by this warp: fixes stage and parity
+  int it_ring = 0;           // TMA iterations issued so far by this warp: fixes stage and parity
   bool ok = true;
 
-  // ---- segments: blocks of one pair that this CTA streams in one go ---------------------------------
-  // [kb_begin, kb_end) are blocks of the fixed share, handed to the warps one at a time through a cursor in
-  // shared memory (warps do not stream equally fast either); with `pool` the warps then go on drawing chunks of
-  // cd blocks from the pair's pool until it is empty.
+  // ---- segments: a run of blocks of one pair that this CTA streams in one go -----------------------
   struct Seg {
     int b, kvh, kb_begin, kb_end, n_blocks, seq_len;
     int slot;                // piece slot, should this segment open a new running state
-    bool pool, valid;
+    bool valid;
   };
   int cur_b = 0;
-  int base = 0;              // share-space index of block 0 of (cur_b, kvh = 0)
+  long long base = 0;        // share-space index of block 0 of (cur_b, kvh = 0)
   while (cur_b < p.B) {
-    const int span = seq_ns(cur_b) * Hkv;
+    const long long span = (long long)seq_ns(cur_b) * Hkv;
     if (g0 < base + span) break;
     base += span;
     ++cur_b;
   }
-  int gcur = g0;
+  long long gcur = g0;
   auto next_static = [&]() {
     Seg sg;
     sg.valid = false;
-    sg.pool = false;
     while (gcur < g1 && cur_b < p.B) {
       const int ns = seq_ns(cur_b);
       if (ns == 0) {
@@ -274,193 +311,102 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
       sg.b = cur_b;
       sg.seq_len = p.seq_lens[cur_b];
       sg.n_blocks = seq_nb(cur_b);
-      sg.kvh = (gcur - base) / ns;
-      sg.kb_begin = (gcur - base) - sg.kvh * ns;
-      sg.kb_end = min(ns, sg.kb_begin + (g1 - gcur));
+      sg.kvh = (int)((gcur - base) / ns);
+      sg.kb_begin = (int)((gcur - base) - (long long)sg.kvh * ns);
+      sg.kb_end = (int)min((long long)ns, (long long)sg.kb_begin + (g1 - gcur));
       sg.slot = blockIdx.x * 2 + (sg.kb_begin == 0 ? 1 : 0);   // slot 1: the piece that starts its pair
       sg.valid = true;
       gcur += (sg.kb_end - sg.kb_begin);
-      sg.pool = gcur >= g1 && seq_nc(cur_b) > 0;    // the share ends here: carry on with this pair's pool
       if (sg.kvh == Hkv - 1 && sg.kb_end == ns) {   // the next segment starts the next sequence
-        base += ns * Hkv;
+        base += (long long)ns * Hkv;
         ++cur_b;
       }
       break;
     }
     return sg;
   };
-  int n_pieces_parked = 0;   // helper slots this CTA has used
-  auto pool_seg = [&](int pair) {
+  auto chunk_seg = [&](int b, int kvh, int c) {
     Seg sg;
-    sg.b = pair / Hkv;
-    sg.kvh = pair % Hkv;
-    sg.n_blocks = seq_nb(sg.b);
-    sg.seq_len = p.seq_lens[sg.b];
-    sg.kb_begin = sg.kb_end = 0;
-    sg.slot = 2 * G + blockIdx.x * kGqaMaxVisits + n_pieces_parked;
-    sg.pool = true;
+    const int nc = seq_nc(b);
+    sg.b = b;
+    sg.kvh = kvh;
+    sg.n_blocks = seq_nb(b);
+    sg.seq_len = p.seq_lens[b];
+    sg.kb_begin = sg.n_blocks - (nc - c) * cd;
+    sg.kb_end = sg.kb_begin + cd;
+    sg.slot = 2 * G + s_hb[b] + kvh * nc + c;
     sg.valid = true;
     return sg;
   };
-  // probe of the pools after `start` (one per thread); stale answers are fine: a pool never refills
-  auto probe = [&](int start, int off, int exclude) {
+  // Find a pool that still has chunks, starting at pair `start`, and draw one.  Uniform over the CTA.
+  // one thread's look at pool start + off + tid; a stale answer is fine, a pool never refills
+  auto probe = [&](int start, int off) {
     bool avail = false;
     if (off + tid < P) {
       const int q = (int)(((long long)start + off + tid) % P);
       const int nc = seq_nc(q / Hkv);
-      if (nc > 0 && q != exclude) avail = ld_relaxed(pool_ctr + q) < nc;
+      if (nc > 0) avail = ld_relaxed(pool_ctr + q) < nc;
     }
     return avail;
   };
-  // Pick a pool that (probably) still has chunks, starting at pair `start`.  Uniform over the CTA.
-  auto pick_pool = [&](int start, bool have_pre, bool pre) {
-    for (int off = 0; off < P; off += kThreads) {
-      const bool avail = (off == 0 && have_pre) ? pre : probe(start, off, -1);
+  // `pre`: the first window's look, taken earlier so that its round trip is over by now
+  auto scan_pools = [&](int start, bool have_pre, bool pre) {
+    Seg sg;
+    sg.valid = false;
+    int off = 0;
+    while (off < P) {
+      const bool avail = (have_pre && off == 0) ? pre : probe(start, off);
+      have_pre = false;
       if (tid == 0) s_flag = INT_MAX;
       __syncthreads();
       if (avail) atomicMin(&s_flag, off + tid);
       __syncthreads();
       const int f = s_flag;
+      if (f == INT_MAX) {
+        off += kThreads;
+        __syncthreads();
+        continue;
+      }
+      const int q = (int)(((long long)start + f) % P);
+      if (tid == 0) s_scan = atomicAdd(pool_ctr + q, 1);
       __syncthreads();
-      if (f != INT_MAX) return (int)(((long long)start + f) % P);
+      const int c = s_scan;
+      __syncthreads();
+      if (c < seq_nc(q / Hkv)) {
+        if (kTrace) ++n_visits;
+        if (kTrace) ++n_drawn;
+        return chunk_seg(q / Hkv, q % Hkv, c);
+      }
+      // somebody else took the pool's last chunk in between: it shows as empty on the next probe
     }
-    return -1;
+    return sg;
   };
 
-  // ---- per-warp loader: which block comes next, and the loads in flight -------------------------------
-  // The blocks of a segment form the CTA's queue: first the blocks of the fixed share, then the chunks drawn
-  // from the pair's pool.  Warps take one block at a time from a cursor in shared memory, so a warp that
-  // streams faster takes more.  The warp that takes queue position t0 + k * cd (t0 = `ahead` chunks before the
-  // end of what the queue holds) draws chunk k from the pool with a global atomic and publishes its first
-  // block a few blocks later, when the atomic's round trip (several microseconds under load) is over; so the
-  // queue is refilled `ahead` chunks before it runs dry and nobody waits for an atomic.
-  int ld_mode = 2;           // 0: taking blocks from the queue, 2: nothing more
-  int ld_base = 0, ld_len = 0, ld_kvh = 0, ld_nc = 0, ld_ns = 0, ld_par = 0, ld_t0 = 0, ld_tag = 0;
-  bool ld_pool = false;
-  const int32_t* ld_bt = p.block_table;
-  int* ld_ctr = pool_ctr;
-  int c_raw = 0;                                 // lane 0: result of this warp's draw in flight
-  bool pd_valid = false;
-  int pd_k = 0, pd_age = 0;
-  int pend_kb = 0, pend_page = 0;
-  bool pend_valid = false;
-  int issued = 0, consumed = 0, my_dyn = 0;
-  int kq0 = 0, kq1 = 0, kq2 = 0;                 // block index of the load in each ring stage
-  const int ahead = max(p.dyn_ahead, 1);
-
-  auto publish_pending = [&]() {
-    if (!pd_valid) return;
-    const int c = __shfl_sync(0xffffffffu, c_raw, 0);          // waits for the atomic if it is still in flight
-    const int base_kb = c < ld_nc ? ld_ns + c * cd : -1;
+  auto issue = [&](const Seg& sg, int ring, int kb, int page) {
+    const int tip = (kb * kBlockTok) % p.page_size;
+    uint8_t* dst = my_smem + (ring % kStages) * kStageBytes;
+    uint64_t* bar = &full_bar[warp][ring % kStages];
+    mbar_expect_tx(bar, kStageBytes);
+    tma_load_4d(dst, &p.k_map, bar, 0, tip, sg.kvh, page);
+    tma_load_4d(dst + 2048, &p.k_map, bar, 64, tip, sg.kvh, page);
+    tma_load_4d(dst + kTileBytes, &p.v_map, bar, 0, tip, sg.kvh, page);
+    tma_load_4d(dst + kTileBytes + 2048, &p.v_map, bar, 64, tip, sg.kvh, page);
+  };
+  // first loads of a segment; called while the previous segment is still being merged, so the
+  // ramp of one segment hides behind the epilogue of the one before
+  auto prologue = [&](const Seg& sg) {
+    const int32_t* bt = p.block_table + (int64_t)sg.b * p.bt_stride;
+    const int my_first = sg.kb_begin + warp;
+    const int my_count = my_first < sg.kb_end ? (sg.kb_end - my_first + kWarps - 1) / kWarps : 0;
+    int pg[kStages];
+#pragma unroll
+    for (int i = 0; i < kStages; ++i)
+      pg[i] = i < my_count ? bt[((my_first + i * kWarps) * kBlockTok) / p.page_size] : 0;
     if (lane == 0) {
-      s_chunk_base[pd_k % kQueue] = base_kb;
-      __threadfence_block();
-      *reinterpret_cast<volatile int*>(&s_chunk_ready[pd_k % kQueue]) = ld_tag + pd_k + 1;
-      if (base_kb < 0) *reinterpret_cast<volatile int*>(&s_closed) = ld_tag;
+#pragma unroll
+      for (int i = 0; i < kStages; ++i)
+        if (i < my_count) issue(sg, it_ring + i, my_first + i * kWarps, pg[i]);
     }
-    pd_valid = false;
-  };
-  auto issue_draw = [&](int k) {
-    publish_pending();                                         // one draw in flight per warp
-    ++n_drawn;
-    if (*reinterpret_cast<volatile int*>(&s_closed) == ld_tag) {
-      if (lane == 0) {                                         // the pool is known to be empty: no atomic needed
-        s_chunk_base[k % kQueue] = -1;
-        __threadfence_block();
-        *reinterpret_cast<volatile int*>(&s_chunk_ready[k % kQueue]) = ld_tag + k + 1;
-      }
-      return;
-    }
-    if (lane == 0) c_raw = atomicAdd(ld_ctr, 1);
-    pd_valid = true;
-    pd_k = k;
-    pd_age = 0;
-  };
-  auto gen_advance = [&]() {
-    pend_valid = false;
-    if (ld_mode == 0) {
-      int i = 0;
-      if (lane == 0) i = atomicAdd(&s_cursor[ld_par], 1);
-      i = __shfl_sync(0xffffffffu, i, 0);
-      if (pd_valid && ++pd_age >= 3) publish_pending();
-      if (ld_pool) {
-        const int t = i - ld_t0;
-        if (t >= 0 && t % cd == 0) issue_draw(t / cd);
-      }
-      if (i < ld_len) {
-        pend_kb = ld_base + i;
-        pend_valid = true;
-      } else if (!ld_pool) {
-        ld_mode = 2;
-      } else {
-        if (p.trace != nullptr && t_static == 0) t_static = now_ns();
-        const int j = (i - ld_len) / cd, off = (i - ld_len) % cd;
-        volatile int* rdy = reinterpret_cast<volatile int*>(&s_chunk_ready[j % kQueue]);
-        if (*rdy != ld_tag + j + 1) {
-          publish_pending();                 // never wait while holding a result that others may be waiting for
-          unsigned spins = 0;
-          while (*rdy != ld_tag + j + 1) {
-            if ((++spins & 255u) == 0u && now_ns() > deadline) {
-              ok = false;
-              break;
-            }
-          }
-        }
-        const int base_kb = ok ? *reinterpret_cast<volatile int*>(&s_chunk_base[j % kQueue]) : -1;
-        if (base_kb < 0) {
-          ld_mode = 2;
-          publish_pending();                 // leaving: hand over what this warp still holds
-        } else {
-          pend_kb = base_kb + off;
-          ++my_dyn;
-          pend_valid = true;
-        }
-      }
-    }
-    // the page id is looked up one block ahead of the copy that needs it, so the (dependent) block-table
-    // load never stalls the warp in front of a copy
-    if (pend_valid) pend_page = ld_bt[(pend_kb * kBlockTok) / p.page_size];
-  };
-  auto issue_pending = [&]() {
-    const int ring = it_ring + issued;
-    const int stage = ring % kStages;
-    if (lane == 0) {
-      const int tip = (pend_kb * kBlockTok) % p.page_size;
-      uint8_t* dst = my_smem + stage * kStageBytes;
-      uint64_t* bar = &full_bar[warp][stage];
-      mbar_expect_tx(bar, kStageBytes);
-      tma_load_4d(dst, &p.k_map, bar, 0, tip, ld_kvh, pend_page);
-      tma_load_4d(dst + 2048, &p.k_map, bar, 64, tip, ld_kvh, pend_page);
-      tma_load_4d(dst + kTileBytes, &p.v_map, bar, 0, tip, ld_kvh, pend_page);
-      tma_load_4d(dst + kTileBytes + 2048, &p.v_map, bar, 64, tip, ld_kvh, pend_page);
-    }
-    if (stage == 0) kq0 = pend_kb;
-    else if (stage == 1) kq1 = pend_kb;
-    else kq2 = pend_kb;
-    ++issued;
-    gen_advance();
-  };
-  // Point the loader at a segment and request its first blocks.  Called while the previous segment is still
-  // being merged, so the ramp of one segment hides behind the epilogue of the one before.
-  auto seg_begin = [&](const Seg& sg) {
-    ld_mode = 0;
-    ld_par ^= 1;
-    ld_tag += 1 << 16;
-    ld_base = sg.kb_begin;
-    ld_len = sg.kb_end - sg.kb_begin;
-    ld_kvh = sg.kvh;
-    ld_pool = sg.pool;
-    ld_nc = seq_nc(sg.b);
-    ld_ns = sg.n_blocks - ld_nc * cd;
-    ld_t0 = ld_len - ahead * cd;
-    ld_bt = p.block_table + (int64_t)sg.b * p.bt_stride;
-    ld_ctr = pool_ctr + (sg.b * Hkv + sg.kvh);
-    issued = consumed = 0;
-    my_dyn = 0;
-    // chunks whose drawing position lies before the start of the queue are drawn right away, one per warp
-    if (ld_pool && ld_t0 < 0 && warp < min((-ld_t0 + cd - 1) / cd, kWarps)) issue_draw(warp);
-    gen_advance();
-    while (issued < kStages && pend_valid) issue_pending();
   };
 
   float* s_o = reinterpret_cast<float*>(smem + kSmemPipe);   // [kWarps][4][kD]: merge buffer, not part of the rings
@@ -469,23 +415,18 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
   Seg cur = next_static();
   if (early_kv) {
     // old KV does not depend on the kernel before us: request the first tiles, then wait for it (q does depend).
-    // A segment that reaches the newest token, or that draws from a pool (the counters are re-armed by the
-    // launch before this one), waits first.
-    const bool wait_first = cur.valid && (cur.kb_end == cur.n_blocks || cur.pool);
-    if (wait_first) asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (cur.valid) seg_begin(cur);
-    if (!wait_first) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // A segment that reaches the newest token waits first: that token's K/V row may still be on its way.
+    const bool touches_newest = cur.valid && cur.kb_end == cur.n_blocks;
+    if (touches_newest) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (cur.valid) prologue(cur);
+    if (!touches_newest) asm volatile("griddepcontrol.wait;" ::: "memory");
   } else if (cur.valid) {
-    seg_begin(cur);
+    prologue(cur);
   }
-  int n_attempts = 0;
+  bool in_static = cur.valid;
   if (!cur.valid && dyn_on) {          // no fixed share (more CTAs than blocks): go straight to the pools
-    const int q = pick_pool(blockIdx.x % max(P, 1), false, false);
-    ++n_attempts;
-    if (q >= 0) {
-      cur = pool_seg(q);
-      seg_begin(cur);
-    }
+    cur = scan_pools(blockIdx.x % max(P, 1), false, false);
+    if (cur.valid) prologue(cur);
   }
 
   // ---- running state of the pair this CTA is accumulating ------------------------------------------
@@ -502,6 +443,7 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
 
   while (cur.valid) {
     const int b = cur.b, kvh = cur.kvh, seq_len = cur.seq_len;
+    const int kb_begin = cur.kb_begin, kb_end = cur.kb_end;
     if (!st_active) {
       st_active = true;
       st_b = b;
@@ -521,17 +463,34 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
         }
       }
     }
-    // a look at the other pools now tells, when this segment is done, where to go next without a round trip
-    const bool pre = cur.pool ? probe(b * Hkv + kvh + 1, 0, b * Hkv + kvh) : false;
+    // What follows this segment?  More of the fixed share, or (when that is done) a chunk of this pair's
+    // pool, drawn now so that the atomic's round trip hides behind the streaming below.
+    const bool static_more = in_static && gcur < g1;
+    const int my_nc = seq_nc(b);
+    const bool drew = !static_more && dyn_on && my_nc > 0;
+    dpar ^= 1;
+    if (drew && tid == 0) s_draw[dpar] = atomicAdd(pool_ctr + (b * Hkv + kvh), 1);
+    // ... and a look at the other pools, in case this one turns out to be empty
+    const bool look = !static_more && dyn_on;
+    const bool pre = look ? probe(b * Hkv + kvh + 1, 0) : false;
 
-    while (consumed < issued) {
-      const int ring = it_ring + consumed;
+    const int32_t* bt = p.block_table + (int64_t)b * p.bt_stride;
+    // page ids are looked up one iteration ahead of the TMA that needs them, so the (dependent)
+    // block-table load never stalls the warp in front of a copy
+    auto page_of = [&](int kb) { return bt[(kb * kBlockTok) / p.page_size]; };
+    const int my_first = kb_begin + warp;
+    const int my_count = my_first < kb_end ? (kb_end - my_first + kWarps - 1) / kWarps : 0;
+    int next_page = kStages < my_count ? page_of(my_first + kStages * kWarps) : 0;
+
+    for (int it = 0; it < my_count; ++it) {
+      const int ring = it_ring + it;
       const int stage = ring % kStages;
+      const int kb = my_first + it * kWarps;
       if (!mbar_wait(&full_bar[warp][stage], (uint32_t)((ring / kStages) & 1), deadline)) {
         ok = false;
         break;
       }
-      const int kb = stage == 0 ? kq0 : (stage == 1 ? kq1 : kq2);
+      if (kTrace && t_first == 0) t_first = now_ns();
       const uint32_t kbase = smem_u32(my_smem + stage * kStageBytes);
       const uint32_t vbase = kbase + kTileBytes;
 
@@ -594,46 +553,45 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
         mma_bf16_16816(o_acc[2 * jj], pa0, 0u, pa2, 0u, r0, r1);
         mma_bf16_16816(o_acc[2 * jj + 1], pa0, 0u, pa2, 0u, r2, r3);
       }
-      ++consumed;
-      // this stage is free again: fetch the block kStages ahead
+      // this stage is free again: fetch the block kStages iterations ahead
       __syncwarp();
-      if (pend_valid) issue_pending();
+      if (lane == 0 && it + kStages < my_count) issue(cur, ring + kStages, kb + kStages * kWarps, next_page);
+      if (it + 1 + kStages < my_count) next_page = page_of(kb + (kStages + 1) * kWarps);
     }
-    it_ring += consumed;
-    dpar ^= 1;
-    if (lane == 0 && my_dyn != 0) atomicAdd(&s_dynblk[dpar], my_dyn);
+    it_ring += my_count;
+    st_blocks += kb_end - kb_begin;
     // The vote makes a timeout of one warp a decision of the whole CTA, so no warp is ever left
     // alone at a barrier; it also orders the next merge after the reads of the previous one and
-    // publishes the warps' pool block counts.
+    // publishes thread 0's drawn chunk.
     if (!__syncthreads_and(ok ? 1 : 0)) {
       ok = false;
       break;
     }
-    if (p.trace != nullptr) t_dyn = now_ns();
-    st_blocks += (cur.kb_end - cur.kb_begin) + s_dynblk[dpar];
+    if (kTrace) {
+      if (in_static) t_static = now_ns();
+      else t_dyn = now_ns();
+    }
     // ---- pick the next segment and start streaming it before the epilogue of this one ---------------
-    Seg nxt = next_static();
-    if (!nxt.valid && dyn_on && n_pieces_parked < kGqaMaxVisits && n_attempts < 2 * kGqaMaxVisits) {
-      const int q = pick_pool(b * Hkv + kvh + 1, cur.pool, pre);
-      ++n_attempts;
-      if (q >= 0) nxt = pool_seg(q);
+    Seg nxt;
+    nxt.valid = false;
+    if (static_more) nxt = next_static();
+    if (!nxt.valid) {
+      in_static = false;
+      if (dyn_on) {
+        const int c = drew ? s_draw[dpar] : INT_MAX;
+        if (c < my_nc) {
+          nxt = chunk_seg(b, kvh, c);
+          if (kTrace) ++n_drawn;
+        } else {
+          nxt = scan_pools(b * Hkv + kvh + 1, look, pre);
+        }
+      }
     }
-    if (nxt.valid) seg_begin(nxt);
-    if (tid == 0) {                       // the next use of these slots is two barriers away
-      s_dynblk[dpar] = 0;
-      s_cursor[dpar] = 0;
-    }
+    if (nxt.valid) prologue(nxt);
 
-    const bool leave = !nxt.valid || nxt.b != st_b || nxt.kvh != st_kvh;
-    if (leave && st_blocks == 0) st_active = false;      // a pool that turned out to be empty: nothing to park
-    if (leave && st_blocks != 0) {
+    if (!nxt.valid || nxt.b != st_b || nxt.kvh != st_kvh) {
       // ---- leave the pair: merge the warps' partials, four heads per round --------------------------
       const bool whole = (st_blocks == st_nb);
-      const bool helper = st_slot >= 2 * G;
-      if (helper) {
-        ++n_pieces_parked;
-        ++n_visits;
-      }
       float* part_o = p.part_o + (size_t)st_slot * 8 * kD;
       float* part_l = p.part_lse + (size_t)st_slot * 8;
       float l_quad = l_run;
@@ -690,7 +648,7 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
         const int pair = st_b * Hkv + st_kvh;
         __syncthreads();
         if (tid == 0) {
-          if (helper) helper_pair[st_slot - 2 * G] = pair + 1;
+          if (st_slot >= 2 * G) helper_flag[st_slot - 2 * G] = 1;
           const int prev = atom_add_acq_rel(done_ctr + pair, st_blocks);
           s_flag = (prev + st_blocks == st_nb);
         }
@@ -699,28 +657,26 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
         if (completes) {
           // ---- this piece completed the pair: fold all of its pieces ---------------------------------
           __syncthreads();                    // everybody has read the verdict before s_flag is reused
-          // pieces from the fixed shares: one per CTA whose share overlaps the pair's fixed blocks
-          const int ns = st_nb - seq_nc(st_b) * cd;
-          int sp0 = 0;
+          // pieces from the fixed shares: one per CTA whose share overlaps the pair's static blocks
+          const int nc = seq_nc(st_b), ns = st_nb - nc * cd;
+          long long sp0 = 0;
           for (int bb = 0; bb < st_b; ++bb) sp0 += seq_ns(bb);
-          sp0 = sp0 * Hkv + st_kvh * ns;
-          const int i0 = sp0 / share, i1 = (sp0 + ns - 1) / share;
+          sp0 = sp0 * Hkv + (long long)st_kvh * ns;
+          const int i0 = (int)(sp0 / share), i1 = (int)((sp0 + ns - 1) / share);
           const int n_fixed = i1 - i0 + 1;
           for (int i = tid; i < n_fixed; i += kThreads) s_list[i] = (i0 + i) * 2 + (i == 0 ? 1 : 0);
           if (tid == 0) s_flag = n_fixed;
           __syncthreads();
-          // pieces parked by CTAs that came over from other pairs
-          if (dyn_on) {
-            const int n_slots = min(G * kGqaMaxVisits, p.max_helper);
-            for (int i = tid; i < n_slots; i += kThreads) {
-              if (ld_relaxed(helper_pair + i) == pair + 1) {
-                const int k = atomicAdd(&s_flag, 1);
-                if (k < kMaxList) s_list[k] = 2 * G + i;
-                helper_pair[i] = 0;                        // ready for the next launch
-              }
+          // pieces parked by CTAs that helped out of this pair's pool
+          const int hb = nc > 0 ? s_hb[st_b] + st_kvh * nc : 0;
+          for (int c = tid; c < nc; c += kThreads) {
+            if (ld_relaxed(helper_flag + hb + c) != 0) {
+              const int k = atomicAdd(&s_flag, 1);
+              if (k < kMaxList) s_list[k] = 2 * G + hb + c;
+              helper_flag[hb + c] = 0;                     // ready for the next launch
             }
-            __syncthreads();
           }
+          __syncthreads();
           const int n_pieces = min(s_flag, kMaxList);
           fold_pieces(FoldArgs{p.part_o, p.part_lse, p.o, p.lse, Hq, p.lse_base2}, s_list, n_pieces, st_b, st_kvh, group,
                       warp, lane);
@@ -751,7 +707,8 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
       }
     }
   } else if (dyn_on && warp == 0) {
-    // the last CTA to leave re-arms the pools for the next launch: nobody draws or probes any more
+    // the last CTA to leave re-arms the pools for the next launch: nobody draws or probes any more (every warp
+    // of this CTA is past the loop above; only this warp waits for the atomic)
     int last = 0;
     if (lane == 0) last = (atom_add_acq_rel(exit_ctr, 1) == G - 1);
     last = __shfl_sync(0xffffffffu, last, 0);
@@ -761,16 +718,17 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
     }
   }
 
-  if (p.trace != nullptr && tid == 0) {
+  if (kTrace && p.trace != nullptr && tid == 0) {
     unsigned smid;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
     unsigned long long* tr = p.trace + (size_t)blockIdx.x * 8;
     tr[0] = t_entry;
-    tr[1] = smid;
-    tr[2] = t_static;      // warp 0 left the fixed share for the pool (0: never)
+    tr[1] = t_first;
+    tr[2] = t_static;
     tr[3] = now_ns();
-    tr[4] = t_dyn;         // end of the last segment's streaming
-    tr[5] = (unsigned long long)n_drawn | ((unsigned long long)n_visits << 32);   // warp 0's chunks, CTA's helper pieces
+    tr[4] = t_dyn;
+    tr[5] = (unsigned long long)n_drawn | ((unsigned long long)n_visits << 32);
+    tr[6] = smid;
   }
 
   // sequences without any token: output 0, LSE -inf (CTA 0 sweeps them)
@@ -787,44 +745,46 @@ __global__ void __launch_bounds__(kThreads, 1) gqa_decode_kernel(const __grid_co
 
 }  // namespace
 
-// Number of CTAs for a launch: one per SM (eight warps each), but never so many that a CTA streams fewer than
-// 64 blocks (its fixed ramp + merge cost is worth about that much streaming).
+// Number of CTAs for a launch: two per SM, but never so many that a CTA streams fewer than
+// 32 blocks (its fixed ramp + merge cost is worth about that much streaming).
 int gqa_pick_ctas(int B, int Hkv, int max_seq_len, int sm_count) {
   const long long blocks = (long long)std::max(B, 1) * Hkv * std::max((max_seq_len + kBlockTok - 1) / kBlockTok, 1);
-  long long ctas = std::min<long long>(sm_count, std::max<long long>(blocks / 64, 1));
+  long long ctas = std::min<long long>(2LL * sm_count, std::max<long long>(blocks / 32, 1));
   return (int)std::min<long long>(ctas, kGqaMaxCtas);
 }
 
-void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int pct_override, int chunk_override,
-                      int ahead_override) {
+void gqa_plan_dynamic(GqaDecodeParams* p, int max_seq_len, int max_helper, int pct_override, int chunk_override) {
   const int nb = std::max(blocks_of(std::max(max_seq_len, 1)), 1);
   const long long blocks = (long long)std::max(p->B, 1) * p->Hkv * nb;
   p->max_helper = std::min(std::max(max_helper, 0), kGqaMaxHelper);
   p->dyn_min_blocks = 64;
-  // a dynamic tail only pays when a CTA's fixed share is long compared with what it keeps drawn ahead
-  int pct = (blocks / std::max(p->ctas, 1) >= 256 && p->B <= kGqaSeqTable) ? 30 : 0;
-  if (pct_override >= 0) pct = std::min(pct_override, 90);
-  const int chunk = chunk_override > 0 ? chunk_override : 8;
-  // a global atomic takes about 4 us when HBM is saturated, in which a CTA streams ~24 blocks: stay ~32 ahead
-  int ahead = ahead_override > 0 ? ahead_override : (32 + chunk - 1) / chunk;
-  ahead = std::min(std::max(ahead, 1), 8);
-  if (p->max_helper < p->ctas * kGqaMaxVisits) pct = 0;    // every CTA needs its helper slots
+  // a dynamic tail only pays when a CTA's fixed share is long compared with a chunk
+  int pct = (blocks / std::max(p->ctas, 1) >= 96 && p->B <= kGqaSeqTable) ? 30 : 0;
+  if (pct_override >= 0) pct = std::min(pct_override, 50);
+  int chunk = chunk_override > 0 ? chunk_override : 20;   // a chunk has a fixed cost (its first loads only start once it is drawn): 16-24 blocks measured best
+  if (pct > 0 && p->max_helper > 0) {
+    // never more chunks than helper slots, whatever the sequence lengths turn out to be
+    const long long worst = (long long)p->B * p->Hkv * ((long long)nb * pct / 100);
+    while ((worst + chunk - 1) / chunk > p->max_helper) chunk += 4;
+  } else {
+    pct = 0;
+  }
   p->dyn_pct = pct;
   p->dyn_chunk = chunk;
-  p->dyn_ahead = ahead;
 }
 
 cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t stream) {
   if (p.B <= 0) return cudaSuccess;
   if (p.Hq % p.Hkv != 0 || p.Hq / p.Hkv > 8 || p.page_size % kBlockTok != 0 || p.ctas < 1 || p.ctas > kGqaMaxCtas ||
-      p.max_helper < 0 || p.max_helper > kGqaMaxHelper || p.dyn_pct < 0 || p.dyn_pct > 90 ||
-      (p.dyn_pct > 0 && (p.dyn_chunk < 1 || p.dyn_ahead < 1 || p.dyn_ahead > 8 || p.max_helper < p.ctas * kGqaMaxVisits)))
+      p.max_helper < 0 || p.max_helper > kGqaMaxHelper || p.dyn_pct < 0 || p.dyn_pct > 50)
     return cudaErrorInvalidValue;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gqa_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(gqa_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
     if (dev < 64) attr_set[dev] = true;
   }
@@ -842,7 +802,8 @@ cudaError_t launch_gqa_decode(const GqaDecodeParams& p, bool pdl, cudaStream_t s
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  return cudaLaunchKernelEx(&cfg, gqa_decode_kernel, p);
+  return p.trace != nullptr ? cudaLaunchKernelEx(&cfg, gqa_decode_kernel<true>, p)
+                            : cudaLaunchKernelEx(&cfg, gqa_decode_kernel<false>, p);
 }
 
 }  // namespace helix

@@ -49,6 +49,10 @@ enum HelixNoAllocStatus {
 //                       token-major page layouts are accepted; the innermost 128 values are contiguous
 //   block_table       : int32 [batch, block_table_stride], seq_lens: int32 [batch] (tokens of this shard)
 //   o                 : bf16 [batch, q_heads, 128] (normalised), lse: fp32 [batch, q_heads]
+//   max_seq_len       : an upper bound of seq_lens (host-side knowledge; the kernel reads the real lengths on
+//                       the device).  It only sizes the launch: batch * kv_heads * ceil(max_seq_len / 16) blocks
+//                       decide how many CTAs are started (two per SM unless the problem is tiny).  A bound that
+//                       is too small costs speed, never correctness; values <= 0 are treated as 1
 //   stream            : a cudaStream_t (0 for the default stream)
 // Returns a HelixNoAllocStatus.  The call is asynchronous with respect to the host.
 int helix_gqa_decode_noalloc(const void* q, int64_t q_stride_batch, int64_t q_stride_head,

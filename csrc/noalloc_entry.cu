@@ -144,7 +144,6 @@ extern "C" __attribute__((visibility("default"))) int helix_gqa_decode_noalloc(
   // fixed shares only: the dynamic tail of the kernel needs more scratch than this array has
   p.dyn_pct = 0;
   p.dyn_chunk = 0;
-  p.dyn_ahead = 1;
   p.dyn_min_blocks = 0;
   p.max_helper = 0;
   p.scale = scale;

@@ -22,6 +22,7 @@ import torch.distributed as dist
 
 from .. import api
 from ..ops import attention, oproj as oproj_mod, reference_math as rm
+from ..utils import env
 
 
 @dataclass

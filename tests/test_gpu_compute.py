@@ -64,15 +64,17 @@ def test_gqa_decode_early_kv_prefetch_under_programmatic_launch(built, monkeypat
     assert (lse - lse_ref).abs().max() < 2e-3
 
 
-@pytest.mark.parametrize("seq_lens,pct,chunk", [([40000], 25, 4), ([8192, 300, 4096], 30, 4), ([20000, 20000], 12, 8),
-                                                ([16384] * 8, 12, 8), ([5000, 0, 70000], 40, 12)])
-def test_gqa_decode_dynamic_tail_matches_fp32_reference(built, monkeypatch, seq_lens, pct, chunk):
+@pytest.mark.parametrize("seq_lens,pct,chunk,ahead", [([40000], 25, 4, 8), ([8192, 300, 4096], 30, 4, 1),
+                                                      ([20000, 20000], 12, 8, 2), ([16384] * 8, 30, 8, 4),
+                                                      ([5000, 0, 70000], 40, 12, 3), ([131072], 50, 2, 2)])
+def test_gqa_decode_dynamic_tail_matches_fp32_reference(built, monkeypatch, seq_lens, pct, chunk, ahead):
     """Part of every long pair is handed out chunk by chunk to whichever CTA finishes its fixed share first; the result
     must not depend on who took what, and the counters must be back at zero for the next launch."""
     from helix_a2a_b200.ops import attention, reference_math as rm
     from helix_a2a_b200.ops.oproj import check_compute_status
     monkeypatch.setenv("HELIX_A2A_ATTN_DYN_PCT", str(pct))
     monkeypatch.setenv("HELIX_A2A_ATTN_DYN_CHUNK", str(chunk))
+    monkeypatch.setenv("HELIX_A2A_ATTN_DYN_AHEAD", str(ahead))
     monkeypatch.setenv("HELIX_A2A_ATTN_DYN_MIN_BLOCKS", "8")
     q, kc, vc, bt, sl = _paged_case(len(seq_lens), 64, 8, seq_lens, seed=3)
     o_ref, lse_ref = rm.paged_decode_attention_reference(q.float(), kc.float(), vc.float(), bt, sl, 1 / math.sqrt(128))

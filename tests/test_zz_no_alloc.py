@@ -73,7 +73,7 @@ def _call(lib, q, kc, vc, bt, sl, max_len):
 
 
 def test_noalloc_entry_matches_regular_op_twice(lib):
-    from helix_a2a_b200.ops import attention
+    from helix_a2a_b200.ops import attention, reference_math as rm
     # two different problems back to back: the second one reuses the scratch the first one dirtied
     for seq_lens, seed in (([3000, 517, 4096, 64], 1), ([2048] * 6 + [1], 2)):
         q, kc, vc, bt, sl = _case(seq_lens, seed)
@@ -82,6 +82,10 @@ def test_noalloc_entry_matches_regular_op_twice(lib):
         torch.cuda.synchronize()
         assert (got_o.float() - want_o.float()).abs().max() < 2e-2
         assert (got_lse - want_lse).abs().max() < 2e-3
+        # and against the plain fp32 attention, so that the check does not lean on the library's own op
+        ref_o, ref_lse = rm.paged_decode_attention_reference(q.float(), kc.float(), vc.float(), bt, sl, 1 / math.sqrt(128))
+        assert (got_o.float() - ref_o).abs().max() < 2e-2
+        assert (got_lse - ref_lse).abs().max() < 2e-3
 
 
 def test_noalloc_entry_rejects_oversized_and_bad_arguments(lib):
