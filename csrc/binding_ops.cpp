@@ -374,66 +374,79 @@ torch::Tensor attn_trace(torch::Tensor like) {
 
 
 // ---- fused exchange + combine + o_proj --------------------------------------------------------------
-// attn_out [B, H, D] bf16, lse [B, H] fp32, w [hidden, (H/cp) * D] bf16 -> y [B, hidden] bf16.
-// emulate: leading [cp] dim on attn_out, lse, w and y; one cooperative launch plays all ranks.
-// Returns (y, x) where x [B, (H/cp) * D] is the combined activation the GEMM consumed.
-std::tuple<torch::Tensor, torch::Tensor> alltoall_combine_oproj(torch::Tensor attn_out, torch::Tensor lse,
-                                                                torch::Tensor w, torch::Tensor workspace,
-                                                                int64_t cp_rank, int64_t cp_size, bool base2,
-                                                                bool emulate, int64_t timeout_ms) {
-  TORCH_CHECK(attn_out.is_cuda() && lse.is_cuda() && w.is_cuda() && workspace.is_cuda(), "inputs must be on CUDA");
-  TORCH_CHECK(attn_out.scalar_type() == at::ScalarType::BFloat16 && w.scalar_type() == at::ScalarType::BFloat16,
-              "attn_out and w must be bfloat16");
+// attn_out [B, H, D] bf16, lse [B, H] fp32, w [hidden, (H/cp) * D] bf16 (or the packed form of it) -> y [B, hidden].
+// emulate: leading [cp] dim on attn_out, lse, w and y; one cooperative launch plays all ranks, and the combined
+// activation x [B, (H/cp) * D] the GEMM consumed is returned as well (it only ever exists in shared memory otherwise).
+std::tuple<torch::Tensor, torch::Tensor> fused_impl(torch::Tensor attn_out, torch::Tensor lse, const torch::Tensor* w,
+                                                    const torch::Tensor* packed, int64_t hidden, torch::Tensor workspace,
+                                                    int64_t cp_rank, int64_t cp_size, bool base2, bool emulate,
+                                                    int64_t timeout_ms) {
+  TORCH_CHECK(attn_out.is_cuda() && lse.is_cuda() && workspace.is_cuda(), "inputs must be on CUDA");
+  TORCH_CHECK(attn_out.scalar_type() == at::ScalarType::BFloat16, "attn_out must be bfloat16");
   TORCH_CHECK(lse.scalar_type() == at::ScalarType::Float, "lse must be float32");
-  TORCH_CHECK(attn_out.is_contiguous() && lse.is_contiguous() && w.is_contiguous(), "inputs must be contiguous");
+  TORCH_CHECK(attn_out.is_contiguous() && lse.is_contiguous(), "inputs must be contiguous");
   const int lead = emulate ? 1 : 0;
-  TORCH_CHECK(attn_out.dim() == 3 + lead && lse.dim() == 2 + lead && w.dim() == 2 + lead, "bad input ranks");
+  TORCH_CHECK(attn_out.dim() == 3 + lead && lse.dim() == 2 + lead, "bad input ranks");
   const int64_t B = attn_out.size(lead), H = attn_out.size(lead + 1), D = attn_out.size(lead + 2);
   TORCH_CHECK(H % cp_size == 0, "heads must divide by cp_size");
-  const int64_t Hl = H / cp_size, K = Hl * D, hidden = w.size(lead);
-  TORCH_CHECK(w.size(lead + 1) == K, "w must be [hidden, (H/cp) * D]");
-  TORCH_CHECK(hidden % 128 == 0 && K % 64 == 0 && (D * 2) % 16 == 0, "hidden % 128, K % 64");
-  TORCH_CHECK(B >= 1 && B <= 256, "1..256 tokens per call");
+  const int64_t Hl = H / cp_size, K = Hl * D;
+  if (w != nullptr) {
+    TORCH_CHECK(w->is_cuda() && w->scalar_type() == at::ScalarType::BFloat16 && w->is_contiguous() && w->dim() == 2 + lead,
+                "w must be a contiguous bfloat16 matrix");
+    hidden = w->size(lead);
+    TORCH_CHECK(w->size(lead + 1) == K, "w must be [hidden, (H/cp) * D]");
+  } else {
+    TORCH_CHECK(!emulate, "packed weights are not supported when one launch plays all ranks");
+    TORCH_CHECK(packed->is_cuda() && packed->scalar_type() == at::ScalarType::Byte && packed->is_contiguous() &&
+                    (size_t)packed->numel() == helix::oproj_packed_bytes((int)hidden, (int)K) &&
+                    reinterpret_cast<uintptr_t>(packed->data_ptr()) % 128 == 0,
+                "packed weight has the wrong size or alignment for [", hidden, ", ", K, "]");
+  }
+  TORCH_CHECK(hidden % 128 == 0 && K % 64 == 0 && (D * 2) % 128 == 0, "hidden % 128, K % 64, head_dim % 64");
+  TORCH_CHECK(B >= 1, "at least one token");
   TORCH_CHECK(workspace.scalar_type() == at::ScalarType::Long && workspace.dim() == 2 && workspace.size(0) == cp_size,
               "workspace must be the [cp_size, elems] int64 tensor");
   const int ranks = emulate ? (int)cp_size : 1;
   TORCH_CHECK(ranks <= helix::kFusedMaxRanks, "at most ", helix::kFusedMaxRanks, " emulated ranks");
-  if (emulate) TORCH_CHECK(attn_out.size(0) == cp_size && w.size(0) == cp_size, "leading [cp] dim expected");
+  if (emulate) TORCH_CHECK(attn_out.size(0) == cp_size && w->size(0) == cp_size, "leading [cp] dim expected");
+  const int splits = helix::fused_pick_splits((int)Hl, (int)D);
+  TORCH_CHECK(splits > 0 && B <= helix::kFusedMaxTokens,
+              "helix: fused exchange+o_proj does not fit this shape (more than ", helix::kFusedMaxTokens,
+              " tokens or a head wider than 512); run alltoall_combine and oproj separately");
   c10::cuda::CUDAGuard guard(attn_out.device());
   auto stream = at::cuda::getCurrentCUDAStream();
   std::vector<int64_t> xs{B, K}, ys{B, hidden};
   if (emulate) { xs.insert(xs.begin(), cp_size); ys.insert(ys.begin(), cp_size); }
-  torch::Tensor x = torch::empty(xs, attn_out.options());
+  torch::Tensor x = emulate ? torch::empty(xs, attn_out.options()) : torch::empty({0}, attn_out.options());
   torch::Tensor y = torch::empty(ys, attn_out.options());
   const int n_pad = (int)((B + 15) / 16 * 16);
-  // split K like the stand-alone GEMM does, as long as the slabs still leave SMs for the exchange
-  int gsplits = emulate ? 1 : helix::oproj_pick_splits((int)hidden, (int)K, helix::device_sm_count());
-  // ... and the exchange keeps at least half a channel per entry (up to 32 channels)
-  const int64_t want_channels = std::max<int64_t>(std::min<int64_t>(B * Hl, 64) / 2, 1);
-  while (gsplits > 1 && (hidden / 128) * gsplits > helix::device_sm_count() - want_channels) --gsplits;
-  Scratch& sc = scratch_for(attn_out.device(), hidden / 128 + 1024,
-                            gsplits > 1 ? (int64_t)helix::oproj_partial_bytes((int)hidden, gsplits, n_pad) / 4 : 0, 0);
+  const int64_t part_floats = splits > 1 ? (int64_t)helix::oproj_partial_bytes((int)hidden, splits, n_pad) / 4 * ranks : 0;
+  Scratch& sc = scratch_for(attn_out.device(), hidden / 128 * ranks + 1024, part_floats, 0);
 
   helix::FusedParams fp{};
   helix::ExchangeParams& p = fp.ex;
   for (int r = 0; r < ranks; ++r) {
     p.io[r].o_src = reinterpret_cast<const uint8_t*>(attn_out.data_ptr()) + (int64_t)r * B * H * D * 2;
     p.io[r].st_src = reinterpret_cast<const uint8_t*>(lse.data_ptr()) + (int64_t)r * B * H * 4;
-    p.io[r].o_dst = reinterpret_cast<uint8_t*>(x.data_ptr()) + (int64_t)r * B * K * 2;
+    p.io[r].o_dst = nullptr;
     p.io[r].st_dst = nullptr;
-    torch::Tensor xr = emulate ? x[r] : x;
-    torch::Tensor wr = emulate ? w[r] : w;
+    fp.x_out[r] = emulate ? reinterpret_cast<__nv_bfloat16*>(x.data_ptr()) + (int64_t)r * B * K : nullptr;
     helix::OprojParams& g = fp.gemm[r];
-    g.w_map = mat_map(wr, 128);
-    g.x_map = mat_map(xr, n_pad);
+    if (w != nullptr) {
+      torch::Tensor wr = emulate ? (*w)[r] : *w;
+      g.w_map = mat_map(wr, 128);
+      g.w_packed = nullptr;
+    } else {
+      g.w_packed = packed->data_ptr<uint8_t>();
+      g.packed_atoms = helix::oproj_packed_atoms((int)K);
+    }
     g.y = reinterpret_cast<__nv_bfloat16*>(y.data_ptr()) + (int64_t)r * B * hidden;
     g.y_stride = hidden;
-    g.partial = gsplits > 1 ? sc.part_a.data_ptr<float>() : nullptr;
-    g.counters = sc.counters.data_ptr<int32_t>() + (sc.counters.numel() - hidden / 128);
+    // every emulated rank needs its own split partials and slab counters
+    g.partial = splits > 1 ? sc.part_a.data_ptr<float>() + (int64_t)r * (part_floats / ranks) : nullptr;
+    g.counters = sc.counters.data_ptr<int32_t>() + (sc.counters.numel() - (hidden / 128) * (r + 1));
     g.error_flag = sc.error_flag.data_ptr<int32_t>();
-    g.tokens = (int)B; g.n_pad = n_pad; g.hidden = (int)hidden; g.K = (int)K; g.splits = gsplits;
-    g.stages = helix::oproj_pick_stages(n_pad);
-    g.atoms = helix::oproj_pick_atoms(n_pad);
+    g.tokens = (int)B; g.n_pad = n_pad; g.hidden = (int)hidden; g.K = (int)K; g.splits = splits;
     g.timeout_ns = timeout_ms > 0 ? (unsigned long long)timeout_ms * 1000000ull : env_timeout_ns();
   }
   p.workspace = reinterpret_cast<uint64_t*>(workspace.data_ptr());
@@ -460,6 +473,20 @@ std::tuple<torch::Tensor, torch::Tensor> alltoall_combine_oproj(torch::Tensor at
               "run alltoall_combine and oproj separately");
   check_cuda(e, "fused exchange+o_proj launch");
   return std::make_tuple(y, x);
+}
+
+std::tuple<torch::Tensor, torch::Tensor> alltoall_combine_oproj(torch::Tensor attn_out, torch::Tensor lse,
+                                                                torch::Tensor w, torch::Tensor workspace,
+                                                                int64_t cp_rank, int64_t cp_size, bool base2,
+                                                                bool emulate, int64_t timeout_ms) {
+  return fused_impl(attn_out, lse, &w, nullptr, 0, workspace, cp_rank, cp_size, base2, emulate, timeout_ms);
+}
+
+torch::Tensor alltoall_combine_oproj_packed(torch::Tensor attn_out, torch::Tensor lse, torch::Tensor packed,
+                                            int64_t hidden, torch::Tensor workspace, int64_t cp_rank, int64_t cp_size,
+                                            bool base2, int64_t timeout_ms) {
+  return std::get<0>(fused_impl(attn_out, lse, nullptr, &packed, hidden, workspace, cp_rank, cp_size, base2, false,
+                                timeout_ms));
 }
 
 int64_t read_error_flag(torch::Tensor like) {
@@ -490,6 +517,10 @@ void register_compute_ops(torch::Library& m) {
       "alltoall_combine_oproj(Tensor attn_out, Tensor lse, Tensor w, Tensor workspace, int cp_rank, int cp_size, bool "
       "base2, bool emulate, int timeout_ms) -> (Tensor, Tensor)",
       &alltoall_combine_oproj);
+  m.def(
+      "alltoall_combine_oproj_packed(Tensor attn_out, Tensor lse, Tensor packed, int hidden, Tensor workspace, int cp_rank, "
+      "int cp_size, bool base2, int timeout_ms) -> Tensor",
+      &alltoall_combine_oproj_packed);
   m.def("read_error_flag(Tensor like) -> int", &read_error_flag);
   m.def("attn_trace(Tensor like) -> Tensor", &attn_trace);
   m.def("clear_error_flag(Tensor like) -> ()", &clear_error_flag);

@@ -1,4 +1,4 @@
-// One kernel for exchange + LSE combine + o_proj: host interface.
+// One kernel for exchange + LSE combine + o_proj: host interface (kernel and design in fused_exchange_oproj.cu).
 #pragma once
 
 #include "exchange.h"
@@ -6,17 +6,29 @@
 
 namespace helix {
 
-constexpr int kFusedMaxRanks = 4;   // ranks one launch can play in single-process emulation
+constexpr int kFusedMaxRanks = 8;     // ranks one launch can play in single-process emulation
+constexpr int kFusedMaxTokens = 64;   // tokens per call (padded to 16): W slice + activation rows must fit shared memory
 
 struct FusedParams {
-  ExchangeParams ex;                 // combine mode, native layout; o_dst is the x buffer of the GEMM
-  OprojParams gemm[kFusedMaxRanks];  // per emulated rank (index 0 in multi-process use); split-K only without emulation
-  int exchange_ctas;                 // CTAs [0, exchange_ctas) exchange, the rest run the GEMM
+  ExchangeParams ex;                 // combine mode, native layout; o_dst is unused
+  // Per emulated rank (index 0 in multi-process use).  `splits` = number of head groups: GEMM CTA (slab, group)
+  // owns heads [group * heads_per_split, +heads_per_split); x_map, stages, atoms and ctas are unused.
+  OprojParams gemm[kFusedMaxRanks];
+  __nv_bfloat16* x_out[kFusedMaxRanks];   // optional [tokens, (H / cp) * D]: the combined activation, for tests
+  int exchange_ctas;                 // CTAs [0, exchange_ctas) only send, the rest receive + combine + multiply
   int gemm_ctas;                     // hidden / 128 * splits
+  int send_warps;                    // sender warps of a sending CTA
+  int heads_per_split;
 };
 
-// Launches the fused kernel; returns cudaErrorNotSupported when the GEMM slabs plus at least one
-// exchange channel do not fit on the device at once (callers then run the two kernels separately).
+// Head groups for a rank that combines `heads_local` heads of `head_dim`: the fewest equal groups whose K-slice is
+// at most 512 wide; 0 when even one head is too wide (the fused kernel then does not apply).
+int fused_pick_splits(int heads_local, int head_dim);
+size_t fused_smem_bytes(int k_slice, int n_pad);
+
+// Launches the fused kernel.  cudaErrorNotSupported: the shape does not fit (more than kFusedMaxTokens tokens, a
+// head wider than 512, more CTAs than the device holds at once, or a call that would fill half a ring); callers
+// then run the exchange and the GEMM as two kernels.
 cudaError_t launch_exchange_oproj(FusedParams fp, int channel_override, bool pdl, cudaStream_t stream,
                                   LaunchInfo* info_out);
 

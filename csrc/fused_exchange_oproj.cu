@@ -1,20 +1,26 @@
 // Helix exchange + LSE combine + o_proj in ONE kernel (sm_100a).
 //
-// The grid is split by role.  CTAs [0, C) run the exchange: sender warps post LL128 lines of the
-// attention output into the peers' rings over NVLink, receiver warps poll the local rings, apply the
-// LSE-weighted combine and write the combined activation rows x[B, K] (bf16, L2 resident); after
-// each row they bump a "rows ready" counter in the local workspace row.  CTAs [C, C + hidden/128)
-// run the o_proj GEMM on tcgen05: each owns one 128-row slab of W_o, starts streaming it with TMA
-// right away (the weights do not depend on the exchange), and only then waits for the counter to
-// reach the number of rows before it fetches x with TMA and issues the UMMAs.  So the weight stream
-// of a layer overlaps the NVLink exchange of the same layer inside one launch, and the combined tile
-// goes from the receive warps to the tensor-core operand without a kernel boundary in between.
-//
-// All CTAs have to be resident at the same time (GEMM CTAs wait for exchange CTAs, which wait for
-// other GPUs): the launcher sizes the grid to at most one CTA per SM and refuses shapes that do not
-// fit.  Every wait is bounded (%globaltimer); on expiry the status block / error flag is set and the
-// kernel returns.  No TMA load uses cluster broadcast; peer memory is only ever written with plain
-// stores, never read.
+// The combined activation never exists in global memory and no CTA waits for another CTA of its own GPU:
+//   * CTAs [0, S) only SEND: their warps read this rank's attention output in place, frame LL128 lines in
+//     registers and post them into the peers' rings over NVLink (plain stores), then leave.
+//   * Every other CTA is a GEMM CTA that owns one 128-row slab of W_o and one group of heads (a K-slice of
+//     at most 512: `heads_per_split` heads of D dims).  It first requests its whole W slice (<= 128 KB, one
+//     bulk copy per 64-wide atom when the weights are pre-packed): the weights do not depend on anything, so
+//     they stream while the other GPUs are still computing.  Then its four warps RECEIVE for themselves:
+//     for every (token, head of the group) they poll the lines of the N - 1 peers in the local rings
+//     (read-only: any number of CTAs may read the same lines), fold them with this rank's own row into the
+//     online LSE-weighted accumulator in registers and store the normalised bf16 row straight into shared
+//     memory in the swizzled K-major layout the tensor core reads - the B operand of the UMMA.  One
+//     fence.proxy.async and a CTA barrier later a single thread issues the UMMAs (D[128, tokens] in TMEM);
+//     the epilogue and the split-K fold over the head groups are those of the stand-alone GEMM.
+//   * The rings have many readers now, so nobody acknowledges lines while reading: every GEMM CTA counts
+//     itself out when it has read its last line, and the one that counts last publishes the consumed line
+//     counts of all rings of the call (locally, and by remote 8-byte stores to the senders).  A call uses a
+//     small fraction of a ring, so senders never wait for that.
+// Senders depend on ring space only (granted by an EARLIER call), receivers on other GPUs' senders only: the
+// CTAs of one GPU need not be resident together, except when one launch plays several ranks for the tests.
+// Every wait is bounded (%globaltimer); on expiry the status block / error flag is set and the kernel
+// returns.  No TMA load uses cluster broadcast; peer memory is only ever written, never read.
 #include "fused.h"
 
 #include <algorithm>
@@ -26,38 +32,34 @@ namespace helix {
 namespace {
 
 using namespace dev;
+using namespace sm100;
 
-constexpr int kReadyOff = 64;    // byte offsets inside the status block of the local row
-constexpr int kGemmSeenOff = 72;
-constexpr int kGemmBarrier = 2;  // named barrier of the 128 GEMM threads
+constexpr int kReadersDoneOff = 64;   // byte offset inside the status block of the local row
+constexpr int kGemmThreads = 128;
+constexpr int kGemmBarrier = 2;       // named barrier of the 128 GEMM threads
+constexpr int kMaxAtoms = 8;          // K-slice of a GEMM CTA: at most 8 atoms of 64 = 512
+constexpr int kMaxRt0 = kMaxCp * 32;  // consumed-line counts cached per CTA: peers x channels
 
-struct ReadyHook {
-  unsigned int* ready;
-  HELIX_D void operator()(int /*e*/, int lane) const {
-    __threadfence();          // the row's stores (all lanes) before the counter
-    __syncwarp();
-    if (lane == 0) atomicAdd(ready, 1u);
-  }
-};
+__device__ __forceinline__ void gemm_sync() { named_barrier(kGemmBarrier, kGemmThreads); }
 
 template <bool BF16, int NIT>
 __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __grid_constant__ FusedParams fp) {
   extern __shared__ __align__(16) uint8_t dyn_smem[];
   __shared__ Control ctl;
+  __shared__ __align__(8) uint64_t w_bar, acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_last;
+  __shared__ unsigned long long s_rt0[kMaxRt0];
+
   const ExchangeParams& p = fp.ex;
   const int rank = p.rank_base + blockIdx.y;
-  uint8_t* my_row = reinterpret_cast<uint8_t*>(p.workspace) + (int64_t)rank * p.row_stride_bytes;
-  const WorkspaceLayout lay = make_layout(p.cp_size, p.sm_count);
-  unsigned int* ready = reinterpret_cast<unsigned int*>(my_row + lay.status_offset + kReadyOff);
-  unsigned int* seen = reinterpret_cast<unsigned int*>(my_row + lay.status_offset + kGemmSeenOff);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
+  const RankIO& io = p.io[blockIdx.y];
+  const int N = p.cp_size, C = p.channels;
 
   if ((int)blockIdx.x < fp.exchange_ctas) {
-    // ------------------------------------------------------------------ exchange + combine role
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int NR = p.recv_warps;
-    const int NS = (int)(blockDim.x >> 5) - NR;
-    const RankIO& io = p.io[blockIdx.y];
-    if (threadIdx.x == 0) {
+    // ------------------------------------------------------------------------------- send role
+    if (tid == 0) {
       ctl.abort = 0;
       ctl.done = 0;
     }
@@ -67,53 +69,246 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
     Ctx cx = make_ctx(p, &ctl, rank, blockIdx.x);
     cx.deadline = globaltimer_ns() + p.timeout_ns;
     load_ring_heads(p, cx);
-    if (warp < NS) {
-      sender_warp<NIT>(p, cx, io, warp, NS, lane);
-    } else {
-      receiver_combine_warp<BF16, NIT>(p, cx, io, warp - NS, NR, lane, reinterpret_cast<float*>(dyn_smem),
-                                       ReadyHook{ready});
-    }
+    const int NS = fp.send_warps;
+    if (warp < NS) sender_warp<NIT>(p, cx, io, warp, NS, lane);
     return;
   }
 
-  // ---------------------------------------------------------------------- o_proj role
-  if (threadIdx.x >= oproj_dev::kThreads) return;
-  pdl_launch_dependents();
+  // --------------------------------------------------------------------------------- GEMM role
+  if (tid >= kGemmThreads) return;
   const OprojParams& gp = fp.gemm[blockIdx.y];
-  const unsigned int rows = (unsigned int)(p.outer * p.inner);
-  const unsigned int n_gemm = (unsigned int)fp.gemm_ctas;
   const int gidx = (int)blockIdx.x - fp.exchange_ctas;
-  oproj_dev::oproj_cta(
-      gp, dyn_smem, gidx / gp.splits, gidx % gp.splits, threadIdx.x,
-      [] { named_barrier(kGemmBarrier, oproj_dev::kThreads); },
-      [&](unsigned long long deadline) {
-        // The counters below are shared by all launches and re-armed by the previous one: under programmatic
-        // launch this CTA may be resident while that launch still runs, so wait for it first (x depends on the
-        // kernel before us anyway; the weight stages were requested above).
-        pdl_wait();
-        // rows written by the combine warps (generic proxy, other SMs) must be complete before TMA reads them
-        unsigned spins = 0;
-        while (true) {
-          unsigned int v;
-          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ready) : "memory");
-          if (v >= rows) break;
-          if ((++spins & 63u) == 0u) {
-            const StatusBlock* sb = reinterpret_cast<const StatusBlock*>(my_row + lay.status_offset);
-            if (ld_volatile_8(&sb->code) != 0ull || sm100::now_ns() > deadline) {
-              StatusBlock* wsb = reinterpret_cast<StatusBlock*>(my_row + lay.status_offset);
-              atomicCAS(&wsb->code, 0ull, (unsigned long long)kTimeoutGemmInput);
-              return false;
-            }
-          }
+  const int m_tile = gidx / gp.splits, split = gidx % gp.splits;
+  const int Hg = fp.heads_per_split;                 // heads of this CTA's K-slice
+  const int D = p.o_bytes >> 1;
+  const int Kc = Hg * D;
+  const int atoms = Kc / 64;
+  const int n_pad = gp.n_pad;
+  const uint32_t atom_a_bytes = 128 * 64 * 2, atom_b_bytes = (uint32_t)n_pad * 64 * 2;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_w = smem;                                   // [atoms][128 x 128 B]
+  uint8_t* smem_x = smem + (size_t)atoms * atom_a_bytes;    // [atoms][n_pad x 128 B]
+  uint32_t tmem_cols = 32;
+  while ((int)tmem_cols < n_pad) tmem_cols <<= 1;
+
+  if (tid == 0) {
+    ctl.abort = 0;
+    ctl.done = 0;
+    mbar_init(&w_bar, 1);
+    mbar_init(&acc_bar, 1);
+    mbar_fence_init();
+    if (gp.w_packed == nullptr) tma_prefetch_desc(&gp.w_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  gemm_sync();
+  tc_fence_after_sync();
+  const uint32_t tmem_d = tmem_slot;
+
+  // the whole W slice of this CTA: nothing it depends on, so it is requested before anything else
+  if (tid == 0) {
+    mbar_expect_tx(&w_bar, (uint32_t)atoms * atom_a_bytes);
+    const int atom0 = split * atoms;
+    for (int a = 0; a < atoms; ++a) {
+      if (gp.w_packed != nullptr)
+        bulk_load_1d(smem_w + (size_t)a * atom_a_bytes,
+                     gp.w_packed + ((size_t)m_tile * gp.packed_atoms + (size_t)(atom0 + a)) * atom_a_bytes, atom_a_bytes,
+                     &w_bar);
+      else
+        tma_load_2d(smem_w + (size_t)a * atom_a_bytes, &gp.w_map, &w_bar, (atom0 + a) * 64, m_tile * 128);
+    }
+  }
+  pdl_launch_dependents();
+  pdl_wait();             // this rank's attention output, and the counts the previous call published
+  Ctx cx = make_ctx(p, &ctl, rank, 0);
+  cx.deadline = globaltimer_ns() + p.timeout_ns;
+  const unsigned long long deadline = cx.deadline;
+
+  // consumed-line count of every ring of this row at the start of the call
+  for (int idx = tid; idx < N * C; idx += kGemmThreads) {
+    const int peer = idx / C, c = idx - peer * C;
+    s_rt0[idx] = peer != rank ? ld_volatile_8(cx.my_row + rinfo_slot(cx.lay, peer, c) + kRinfoTailOff) : 0ull;
+  }
+  gemm_sync();
+
+  // ---- receive + combine: the rows of this CTA's head group, straight into the B operand ----------------
+  const int payload_words = p.st_words + (p.o_bytes >> 3);
+  const int L = ll128::lines_for_words(payload_words);
+  const int nchunks = L * kChunksPerLine;
+  const int Hl = p.inner;
+  bool alive = true;
+  for (int ent = warp; ent < p.outer * Hg && alive; ent += kGemmThreads / 32) {
+    const int b = ent / Hg, hg = ent - b * Hg;
+    const int hl = split * Hg + hg;
+    const int e = b * Hl + hl;
+    const int c = e % C, i = e / C;
+    cx.channel = c;
+    Acc<NIT> acc;
+    acc.init();
+    uint64_t lo[NIT], hi[NIT];
+    load_message<NIT>(p, msg_src(p, io, e, rank), 0, nchunks, payload_words, lane, lo, hi);
+    acc.template add<BF16>(ingest_lse(__shfl_sync(kFull, lo[0], 0), p.stats_mode, p.base2), lo, hi);
+    for (int j = 0; j < N - 1; ++j) {
+      const int peer = (rank + N - 1 - j) % N;
+      const uint64_t q0 = s_rt0[peer * C + c] + (uint64_t)i * L;
+      const uint8_t* ring = cx.my_row + ring_offset(cx.lay, peer, c);
+      if (!poll_message<NIT>(cx, ring, q0, 0, nchunks, lane, lo, hi)) {
+        if (lane == 0) report(cx, kTimeoutRecv, peer, e);
+        alive = false;
+        break;
+      }
+      acc.template add<BF16>(ingest_lse(__shfl_sync(kFull, lo[0], 0), p.stats_mode, p.base2), lo, hi);
+    }
+    if (!alive) break;
+    const float inv = acc.s > 0.f ? 1.0f / acc.s : 0.f;
+    uint8_t* xg = (fp.x_out[blockIdx.y] != nullptr && m_tile == 0)
+                      ? reinterpret_cast<uint8_t*>(fp.x_out[blockIdx.y]) + ((int64_t)b * Hl + hl) * p.o_bytes
+                      : nullptr;
+#pragma unroll
+    for (int it = 0; it < NIT; ++it) {
+      const int ch = it * 32 + lane;
+      if (ch < nchunks) {
+        const ll128::ChunkMap m = ll128::chunk_map(ch);
+        float f[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = acc.v[it][k] * inv;
+        const int w0 = m.first, w1 = m.first + 1;
+        // payload word w of the row = bytes [8 (w - st_words), +8) of the head's D * 2 bytes
+        auto put = [&](int w, const float* v) {
+          if (w < p.st_words || w >= payload_words) return;
+          const uint64_t packed = pack4<BF16>(v);
+          const int byte = hg * p.o_bytes + 8 * (w - p.st_words);       // inside the CTA's K-slice of row b
+          const int atom = byte >> 7, inb = byte & 127;
+          const uint32_t off = (uint32_t)atom * atom_b_bytes + swz128((uint32_t)b, (uint32_t)(inb >> 4)) + (inb & 15);
+          *reinterpret_cast<uint64_t*>(smem_x + off) = packed;
+          if (xg != nullptr) *reinterpret_cast<uint64_t*>(xg + 8 * (w - p.st_words)) = packed;
+        };
+        put(w0, f);
+        if (!m.has_flag) put(w1, f + 4);
+      }
+    }
+  }
+  // rows written by ordinary stores must be visible to the tensor core's (asynchronous-proxy) reads
+  fence_proxy_async_smem();
+  gemm_sync();
+  const bool bad = *reinterpret_cast<volatile int*>(&ctl.abort) != 0;
+
+  // this CTA has read its last line: count it out; the last one of the call publishes the consumed counts
+  if (warp == 0) {
+    unsigned int* readers = reinterpret_cast<unsigned int*>(cx.my_row + cx.lay.status_offset + kReadersDoneOff);
+    int last = 0;
+    if (lane == 0) {
+      __threadfence();
+      last = (atomicAdd(readers, 1u) == (unsigned)fp.gemm_ctas - 1u);
+    }
+    last = __shfl_sync(kFull, last, 0);
+    if (last) {
+      if (!bad) {
+        const int E = p.outer * p.inner;
+        for (int idx = lane; idx < N * C; idx += 32) {
+          const int peer = idx / C, c = idx - peer * C;
+          if (peer == rank) continue;
+          const uint64_t t_new = s_rt0[idx] + (uint64_t)entries_of_channel(E, C, c) * L;
+          st_volatile_8(cx.my_row + rinfo_slot(cx.lay, peer, c) + kRinfoTailOff, t_new);
+          st_volatile_8(cx.ws + (int64_t)peer * cx.stride + sinfo_slot(cx.lay, rank, c) + kSinfoTailOff, t_new);
         }
-        asm volatile("fence.proxy.async;" ::: "memory");
-        // the last GEMM CTA to get here re-arms both counters for the next launch
-        if (atomicAdd(seen, 1u) == n_gemm - 1u) {
-          *reinterpret_cast<volatile unsigned int*>(seen) = 0u;
-          *reinterpret_cast<volatile unsigned int*>(ready) = 0u;
+      }
+      __syncwarp();
+      if (lane == 0) *reinterpret_cast<volatile unsigned int*>(readers) = 0u;    // re-armed for the next call
+    }
+  }
+
+  // ---- MMA: D[128, n_pad] = W slab (K-slice) x rows^T ---------------------------------------------------
+  bool ok = !bad;
+  if (warp == 1 && lane == 0 && ok) {
+    if (!mbar_wait(&w_bar, 0, deadline)) {
+      atomicCAS(gp.error_flag, 0, (int)kTimeoutMbarrier);
+      *reinterpret_cast<volatile int*>(&ctl.abort) = 1;
+    } else {
+      tc_fence_after_sync();
+      const uint32_t idesc = umma_idesc_bf16(128, n_pad);
+      const uint32_t a_addr = smem_u32(smem_w), b_addr = smem_u32(smem_x);
+      for (int a = 0; a < atoms; ++a) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_bf16(tmem_d, umma_desc_k_sw128(a_addr + a * atom_a_bytes + k * 32),
+                    umma_desc_k_sw128(b_addr + a * atom_b_bytes + k * 32), idesc, (a | k) != 0);
+      }
+      umma_commit(&acc_bar);
+    }
+  }
+  // ---- epilogue (all four warps): warp w owns TMEM lanes 32w .. 32w + 31 = rows of the W slab ----------------
+  __syncwarp();
+  if (ok) {
+    int good = 1;
+    if (lane == 0) {
+      unsigned spins = 0;
+      while (!mbar_try_wait(&acc_bar, 0)) {
+        if ((++spins & 63u) == 0u && (*reinterpret_cast<volatile int*>(&ctl.abort) || now_ns() > deadline)) {
+          good = 0;
+          break;
         }
-        return true;
-      });
+      }
+    }
+    good = __shfl_sync(kFull, good, 0);
+    ok = good != 0;
+    if (!ok && lane == 0) atomicCAS(gp.error_flag, 0, (int)kTimeoutMbarrier);
+  }
+  tc_fence_after_sync();
+  const int row = warp * 32 + lane;
+  const int hcol = m_tile * 128 + row;
+  float* part = gp.splits > 1 ? gp.partial + ((size_t)(m_tile * gp.splits + split) * n_pad) * 128 : nullptr;
+  if (ok) {
+    for (int c0 = 0; c0 < n_pad; c0 += 16) {
+      uint32_t v[16];
+      tmem_ld_32x32b_x16(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int tok = c0 + j;
+        if (gp.splits == 1) {
+          if (tok < gp.tokens) gp.y[(int64_t)tok * gp.y_stride + hcol] = __float2bfloat16(__uint_as_float(v[j]));
+        } else {
+          part[(size_t)tok * 128 + row] = __uint_as_float(v[j]);
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  gemm_sync();
+  if (warp == 1) tmem_dealloc(tmem_d, tmem_cols);
+  if (!ok) {
+    // the weight copies may still be on their way into this CTA's shared memory: give them a bounded moment
+    if (tid == 0) mbar_wait(&w_bar, 0, now_ns() + 2000000ull);
+    return;
+  }
+  if (gp.splits == 1) return;
+
+  // ---- the head groups of a slab are K splits: the last CTA of the slab sums them -------------------------
+  __threadfence();
+  gemm_sync();
+  if (tid == 0) s_last = (atomicAdd(&gp.counters[m_tile], 1) == gp.splits - 1);
+  gemm_sync();
+  if (!s_last) return;
+  __threadfence();
+  const float* base = gp.partial + (size_t)m_tile * gp.splits * n_pad * 128;
+  for (int tok0 = 0; tok0 < gp.tokens; tok0 += 8) {
+    float accs[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) accs[j] = 0.f;
+    for (int s = 0; s < gp.splits; ++s) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)   // rows of the partial are padded to n_pad (a multiple of 16): always in bounds
+        accs[j] += __ldcg(base + ((size_t)s * n_pad + tok0 + j) * 128 + tid);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (tok0 + j < gp.tokens) gp.y[(int64_t)(tok0 + j) * gp.y_stride + m_tile * 128 + tid] = __float2bfloat16(accs[j]);
+  }
+  if (tid == 0) gp.counters[m_tile] = 0;
 }
 
 using FusedFn = void (*)(FusedParams);
@@ -125,53 +320,68 @@ FusedFn pick(bool bf16) {
 
 }  // namespace
 
+int fused_pick_splits(int heads_local, int head_dim) {
+  // the smallest number of head groups whose K-slice fits a CTA (512), with equal groups
+  for (int s = 1; s <= heads_local; ++s)
+    if (heads_local % s == 0 && (heads_local / s) * head_dim <= 64 * kMaxAtoms) return s;
+  return 0;
+}
+
+size_t fused_smem_bytes(int k_slice, int n_pad) { return (size_t)(k_slice / 64) * (128 + n_pad) * 128 + 1024; }
+
 cudaError_t launch_exchange_oproj(FusedParams fp, int channel_override, bool pdl, cudaStream_t stream,
                                   LaunchInfo* info_out) {
   ExchangeParams& p = fp.ex;
   const int E = p.outer * p.inner;
   if (E <= 0) return cudaSuccess;
   if (p.mode != kModeCombine || p.ranks_in_launch < 1 || p.ranks_in_launch > kFusedMaxRanks) return cudaErrorInvalidValue;
+  const OprojParams& g0 = fp.gemm[0];
+  const int D = p.o_bytes / 2;
+  if (g0.splits < 1 || p.inner % g0.splits != 0 || (D * 2) % 128 != 0) return cudaErrorInvalidValue;
+  const int Hg = p.inner / g0.splits, Kc = Hg * D;
+  if (Kc > 64 * kMaxAtoms || Kc % 64 != 0 || g0.n_pad > kFusedMaxTokens || g0.n_pad % 16 != 0) return cudaErrorNotSupported;
   for (int r = 0; r < p.ranks_in_launch; ++r)
-    if (fp.gemm[r].splits < 1 || (fp.gemm[r].splits > 1 && (fp.gemm[r].partial == nullptr || p.ranks_in_launch > 1)))
-      return cudaErrorInvalidValue;
+    if (fp.gemm[r].splits != g0.splits || (g0.splits > 1 && fp.gemm[r].partial == nullptr)) return cudaErrorInvalidValue;
+  fp.heads_per_split = Hg;
+
   LaunchInfo li = plan_launch(p, channel_override);
   FusedFn fn = nullptr;
-  int nit = 0;
-  if (li.iters <= 1) { fn = pick<1>(p.is_bf16); nit = 1; }
-  else if (li.iters <= 2) { fn = pick<2>(p.is_bf16); nit = 2; }
-  else if (li.iters <= 3) { fn = pick<3>(p.is_bf16); nit = 3; }
-  else if (li.iters <= 5) { fn = pick<5>(p.is_bf16); nit = 5; }
+  if (li.iters <= 1) fn = pick<1>(p.is_bf16);
+  else if (li.iters <= 2) fn = pick<2>(p.is_bf16);
+  else if (li.iters <= 3) fn = pick<3>(p.is_bf16);
+  else if (li.iters <= 5) fn = pick<5>(p.is_bf16);
   else return cudaErrorNotSupported;
 
-  const int threads = 32 * (li.send_warps + li.recv_warps);
-  size_t smem_ex = li.group_warps > 1
-                       ? (size_t)(li.recv_warps / li.group_warps) * 2 * (li.group_warps - 1) * (nit * 8 * 32 + 4) * sizeof(float)
-                       : 0;
-  size_t smem = std::max<size_t>(smem_ex, (size_t)oproj_smem_bytes(fp.gemm[0].n_pad, fp.gemm[0].stages));
+  const int gemm_ctas = g0.hidden / 128 * g0.splits;
+  const int threads = std::max(32 * li.send_warps, kGemmThreads);
+  const size_t smem = fused_smem_bytes(Kc, g0.n_pad);
   cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  int per_sm = 0, sms = p.sm_count;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, std::max(threads, 128), smem);
+  int per_sm = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, threads, smem);
   if (e != cudaSuccess) return e;
-  const int capacity = per_sm * sms / p.ranks_in_launch;     // CTAs one rank may use
-  const int gemm_ctas = fp.gemm[0].hidden / 128 * fp.gemm[0].splits;
+  if (per_sm < 1) return cudaErrorNotSupported;
+  const int capacity = per_sm * p.sm_count / p.ranks_in_launch;     // CTAs one rank may have resident
+  // Sender CTAs first, then every GEMM CTA resident at once: a GEMM CTA that starts late has not prefetched its
+  // weights (and in a launch that plays several ranks it would be waited for by the others).
   if (capacity - gemm_ctas < 1) return cudaErrorNotSupported;
-  li.channels = std::min(li.channels, capacity - gemm_ctas);
+  li.channels = std::max(1, std::min({li.channels, capacity - gemm_ctas, 32}));
+  if (p.cp_size * li.channels > kMaxRt0) return cudaErrorNotSupported;
+  // the consumed counts are only published at the end of the call: a call must fit well inside a ring
+  const int L = li.lines_per_message;
+  if ((int64_t)ceil_div(E, li.channels) * L > kRingLines / 2) return cudaErrorNotSupported;
 
   p.channels = li.channels;
-  p.recv_warps = li.recv_warps;
-  p.group_warps = li.group_warps;
-  const int L = li.lines_per_message;
-  const int per_channel = ceil_div(E, li.channels);
-  if ((int64_t)per_channel * L <= kRingLines / 2) p.rounds_per_publish = 0;
-  else p.rounds_per_publish = std::max(1, (kRingLines / 4) / ((li.recv_warps / li.group_warps) * L));
-  if (L > kRingLines / 8) return cudaErrorInvalidValue;
+  p.recv_warps = 0;
+  p.group_warps = 1;
+  p.rounds_per_publish = 0;
   fp.exchange_ctas = li.channels;
   fp.gemm_ctas = gemm_ctas;
+  fp.send_warps = li.send_warps;
 
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(li.channels + gemm_ctas, p.ranks_in_launch, 1);
-  cfg.blockDim = dim3(std::max(threads, 128), 1, 1);
+  cfg.blockDim = dim3(threads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];

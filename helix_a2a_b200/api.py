@@ -166,14 +166,16 @@ def alltoall_combine(attn_out: torch.Tensor, lse: torch.Tensor, workspace: torch
     return (out, glse) if return_lse else out
 
 
-def alltoall_combine_oproj(attn_out: torch.Tensor, lse: torch.Tensor, w_o: torch.Tensor, workspace: torch.Tensor,
+def alltoall_combine_oproj(attn_out: torch.Tensor, lse: torch.Tensor, w_o, workspace: torch.Tensor,
                            cp_rank: int, cp_size: int, *, base2: bool = False, timeout_ms: int = 0) -> torch.Tensor:
     """Exchange + LSE combine + o_proj in one kernel launch.
 
-    ``attn_out [B, H, D]`` (bf16), ``lse [B, H]`` (fp32), ``w_o [hidden, (H/N) * D]`` (this rank's
-    K-slice of the o_proj weight, bf16) -> ``y [B, hidden]`` (this rank's partial sum).  The weight
-    slabs start streaming before the exchange has finished.  On CPU tensors, or when the shape does
-    not fit one co-resident grid, the two steps run one after the other.
+    ``attn_out [B, H, D]`` (bf16), ``lse [B, H]`` (fp32), ``w_o [hidden, (H/N) * D]`` (this rank's K-slice of the
+    o_proj weight, bf16, or its ``ops.oproj.PackedOprojWeight`` form) -> ``y [B, hidden]`` (this rank's partial
+    sum).  GEMM CTAs request their weights first, then receive and combine the rows of their own heads straight
+    into the tensor-core operand in shared memory; the combined activation never goes through global memory.
+    On CPU tensors, or when the shape does not fit (more than 64 tokens, a head wider than 512 dims, more GEMM
+    CTAs than SMs), the exchange and the GEMM run as two launches.
     """
     from .ops import oproj as _oproj
     B = attn_out.shape[0]
@@ -182,6 +184,9 @@ def alltoall_combine_oproj(attn_out: torch.Tensor, lse: torch.Tensor, w_o: torch
         return _oproj.oproj(x.reshape(B, -1), w_o)
     from .ops._ext import ops
     try:
+        if isinstance(w_o, _oproj.PackedOprojWeight):
+            return ops().alltoall_combine_oproj_packed(attn_out, lse, w_o.packed, w_o.hidden, workspace, cp_rank, cp_size,
+                                                       base2, timeout_ms)
         y, _ = ops().alltoall_combine_oproj(attn_out, lse, w_o, workspace, cp_rank, cp_size, base2, False, timeout_ms)
         return y
     except RuntimeError as e:

@@ -102,7 +102,7 @@ class HelixDecodeStack:
                                           scale=self.scale, max_seq_len=self.local_ctx, kv_stable=True)
         if self.cp_size > 1 and self.fuse_oproj:
             # exchange + combine + o_proj in one launch: W_o streams while the exchange is in flight
-            return api.alltoall_combine_oproj(o, lse, self.w_o[l], self.workspace, self.cp_rank, self.cp_size)
+            return api.alltoall_combine_oproj(o, lse, self._oproj_weight(l), self.workspace, self.cp_rank, self.cp_size)
         if self.cp_size > 1:
             x = api.alltoall_combine(o, lse, self.workspace, self.cp_rank, self.cp_size)
         else:

@@ -102,6 +102,48 @@ def main():
             ok &= (y.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
         check(f"one-kernel exchange+combine+o_proj B={B} hidden={hidden}", ok)
 
+    # the same through pre-packed weights, alternating with plain exchange calls on the same rings, then
+    # replayed from a CUDA graph; says whether the one-kernel path really ran or the two-launch fall-back did
+    from helix_a2a_b200.ops.oproj import prepack_weight
+    B, H, D, hidden = 8, 64, 128, 2048
+    if H % world == 0:
+        g = torch.Generator(device="cuda").manual_seed(77)
+        outs = torch.randn(world, B, H, D, device="cuda", generator=g).bfloat16()
+        lses = torch.randn(world, B, H, device="cuda", generator=g) * 2
+        w_all = (torch.randn(world, hidden, (H // world) * D, device="cuda", generator=g) * 0.05).bfloat16()
+        o_in, l_in, packed = outs[rank].contiguous(), lses[rank].contiguous(), prepack_weight(w_all[rank].contiguous())
+        try:
+            torch.ops.helix_a2a_b200.alltoall_combine_oproj_packed(o_in, l_in, packed.packed, hidden, ws, rank, world, False, 0)
+            fused_ran = True
+        except RuntimeError as e:
+            fused_ran = False
+            assert "does not fit" in str(e), e
+        if rank == 0:
+            print(f"  one-kernel path at cp={world}: {'runs' if fused_ran else 'does not fit, two launches'}", flush=True)
+        xr = rm.head_scatter_combine_reference(outs, lses)[rank].reshape(B, -1)
+        ref = rm.oproj_reference(xr.bfloat16(), w_all[rank])
+        tol = 3e-2 * max(1.0, ref.abs().max().item())
+        ok = True
+        for it in range(6):
+            if it % 2:
+                helix.alltoall_combine(o_in, l_in, ws, rank, world)
+            y = helix.alltoall_combine_oproj(o_in, l_in, packed, ws, rank, world)
+            ok &= (y.float() - ref).abs().max().item() < tol
+        stf = torch.cuda.Stream()
+        stf.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stf):
+            gf = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gf, stream=stf):
+                for _ in range(20):
+                    y_g = helix.alltoall_combine_oproj(o_in, l_in, packed, ws, rank, world)
+        torch.cuda.current_stream().wait_stream(stf)
+        dist.barrier()
+        for _ in range(20):
+            gf.replay()
+        torch.cuda.synchronize()
+        ok &= (y_g.float() - ref).abs().max().item() < tol
+        check("exchange+combine+o_proj with packed weights, mixed with plain calls, 400 graph-replayed calls", ok)
+
     # many calls back to back without re-init (rings wrap), ranks deliberately skewed
     g = torch.Generator(device="cuda").manual_seed(5)
     outs = torch.randn(world, 16, 64, 128, device="cuda", generator=g).bfloat16()
