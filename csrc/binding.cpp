@@ -160,6 +160,10 @@ std::tuple<torch::Tensor, torch::Tensor> alltoall_impl(torch::Tensor partial_o, 
   p.is_bf16 = partial_o.scalar_type() == at::ScalarType::BFloat16;
   p.mode = helix::kModeExchange;
   p.skip_peer_mask = (uint32_t)skip_peer_mask;
+  // debug bounds checks: one rank's byte extents; checked per message on the device with HELIX_A2A_DEBUG=1
+  p.o_src_bytes = p.o_dst_bytes = o_rank_bytes;
+  p.st_src_bytes = p.st_dst_bytes = s_rank_bytes;
+  p.debug_checks = env_debug() ? 1 : 0;
   launch(p, timeout_ms);
   return std::make_tuple(o_out, s_out);
 }
@@ -317,6 +321,11 @@ std::tuple<torch::Tensor, torch::Tensor> alltoall_combine(torch::Tensor attn_out
   p.mode = helix::kModeCombine;
   p.stats_mode = (int)stats_mode;
   p.base2 = base2 ? 1 : 0;
+  p.o_src_bytes = in_o_rank_bytes;
+  p.st_src_bytes = in_s_rank_bytes;
+  p.o_dst_bytes = out_rank_bytes;
+  p.st_dst_bytes = lse_rank_bytes;
+  p.debug_checks = env_debug() ? 1 : 0;
   p.skip_peer_mask = (uint32_t)skip_peer_mask;
   launch(p, timeout_ms);
   return std::make_tuple(out, lse_out);

@@ -62,6 +62,9 @@ struct ExchangeParams {
   int recv_warps;       // receiver warps per CTA
   int group_warps;      // combine: receiver warps that share one entry (each polls a subset of peers)
   int rounds_per_publish;  // 0: publish consumed counts only at the end of the call
+  // debug bounds checks (bounds.cuh): byte extents of one rank's tensors, 0 = not recorded
+  int64_t o_src_bytes, st_src_bytes, o_dst_bytes, st_dst_bytes;
+  int debug_checks;         // check every message's source / destination span against the extents
   uint32_t skip_peer_mask;  // debug / fault tests: sender silently skips these peers
   unsigned long long timeout_ns;
 };

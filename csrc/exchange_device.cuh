@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "bounds.cuh"
 #include "exchange.h"
 #include "fifo.cuh"
 #include "ll128.cuh"
@@ -113,12 +114,23 @@ struct MsgSrc {
 };
 
 HELIX_D MsgSrc msg_src(const ExchangeParams& p, const RankIO& io, int e, int peer) {
-  int b = e / p.inner;
-  int hl = e - b * p.inner;
   MsgSrc s;
-  s.o = io.o_src + b * p.o_sb + peer * p.o_sp + hl * p.o_sh;
-  s.st = io.st_src + b * p.st_sb + peer * p.st_sp + hl * p.st_sh;
+  s.o = io.o_src + bounds::src_o_off(p, e, peer);
+  s.st = io.st_src + bounds::src_st_off(p, e, peer);
   return s;
+}
+
+// Debug mode: may message (e, peer) be read / may its row be written?  A span that does not fit the caller's
+// tensor is reported once (kBadArgument) and the caller skips the access.
+HELIX_D bool check_source(const ExchangeParams& p, const Ctx& cx, int e, int peer, int lane) {
+  if (!p.debug_checks || bounds::source_ok(p, e, peer)) return true;
+  if (lane == 0) report(cx, kBadArgument, peer, e);
+  return false;
+}
+HELIX_D bool check_dest(const ExchangeParams& p, const Ctx& cx, const RankIO& io, int e, int peer, int lane) {
+  if (!p.debug_checks || bounds::dest_ok(p, e, peer, io.st_dst != nullptr)) return true;
+  if (lane == 0) report(cx, kBadArgument, peer, e);
+  return false;
 }
 
 // payload word w of a message, read from the user's tensors
@@ -299,6 +311,10 @@ HELIX_D void sender_warp(const ExchangeParams& p, const Ctx& cx, const RankIO& i
     const uint64_t head = cx.ctl->head[peer];
     uint64_t tail = ld_volatile_8(sinfo + kSinfoTailOff);
     bool ok = true;
+    if (p.debug_checks) {                      // debug: every message this warp is about to read must fit the tensors
+      for (int i = k; i < n_mine && ok; i += K) ok = check_source(p, cx, c + i * C, peer, lane);
+      if (!ok) continue;                       // reported; nothing is read or sent for this peer
+    }
     uint64_t lo[NIT], hi[NIT];
     if (single_slab && k < n_mine) load_message<NIT>(p, msg_src(p, io, c + k * C, peer), 0, nchunks, payload_words, lane, lo, hi);
     for (int i = k; i < n_mine && ok; i += K) {
@@ -408,6 +424,10 @@ HELIX_D void receiver_exchange_warp(const ExchangeParams& p, const Ctx& cx, cons
       uint8_t* sd = io.st_dst + e * p.sd_se + peer * p.sd_sp;
       const uint64_t q0 = __shfl_sync(kFull, rtail0, peer) + (uint64_t)i * L;
       const uint8_t* ring = cx.my_row + ring_offset(cx.lay, peer, c);
+      if (!check_dest(p, cx, io, e, peer, lane) || (peer == rank && !check_source(p, cx, e, rank, lane))) {
+        alive = false;                         // debug: the row would land outside the caller's tensor
+        continue;
+      }
       const MsgSrc self = msg_src(p, io, e, rank);
       for (int chunk0 = 0; chunk0 < nchunks; chunk0 += NIT * 32) {
         uint64_t lo[NIT], hi[NIT];
@@ -473,6 +493,7 @@ HELIX_D void receiver_combine_warp(const ExchangeParams& p, const Ctx& cx, const
     const int e = c + i * C;
     Acc<NIT> acc;
     acc.init();
+    if (have && alive && (!check_source(p, cx, e, rank, lane) || !check_dest(p, cx, io, e, 0, lane))) alive = false;
     if (have && alive) {
       uint64_t lo[NIT], hi[NIT];
       if (k == 0) {  // this rank's own contribution comes straight from its attention output

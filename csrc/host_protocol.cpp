@@ -18,6 +18,7 @@
 #include <vector>
 
 #include "fifo.cuh"
+#include "bounds.cuh"
 #include "ll128.cuh"
 
 using namespace helix;
@@ -217,6 +218,22 @@ int helix_model_run(int cp, int calls, const int* entries_per_call, int payload_
   }
   if (lines_moved) *lines_moved = moved;
   return 0;
+}
+
+// Debug bounds checks of the exchange (bounds.cuh): number of messages of a launch whose source or destination
+// span leaves the recorded extents.  strides / extents in bytes; mode 0 = exchange, 1 = combine.
+int helix_bounds_violations(int cp, int outer, int inner, int mode, int o_bytes, int st_words, int lse_scalar,
+                            long long o_sb, long long o_sp, long long o_sh, long long st_sb, long long st_sp,
+                            long long st_sh, long long od_se, long long od_sp, long long sd_se, long long sd_sp,
+                            long long o_src_bytes, long long st_src_bytes, long long o_dst_bytes,
+                            long long st_dst_bytes, int has_st_dst) {
+  helix::ExchangeParams p{};
+  p.cp_size = cp; p.outer = outer; p.inner = inner; p.mode = mode; p.o_bytes = o_bytes; p.st_words = st_words;
+  p.lse_scalar = lse_scalar;
+  p.o_sb = o_sb; p.o_sp = o_sp; p.o_sh = o_sh; p.st_sb = st_sb; p.st_sp = st_sp; p.st_sh = st_sh;
+  p.od_se = od_se; p.od_sp = od_sp; p.sd_se = sd_se; p.sd_sp = sd_sp;
+  p.o_src_bytes = o_src_bytes; p.st_src_bytes = st_src_bytes; p.o_dst_bytes = o_dst_bytes; p.st_dst_bytes = st_dst_bytes;
+  return helix::bounds::count_violations(p, has_st_dst != 0);
 }
 
 }  // extern "C"

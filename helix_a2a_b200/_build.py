@@ -78,7 +78,8 @@ def build_host_lib(force: bool = False) -> Path:
     src = CSRC / "host_protocol.cpp"
     if force or _stale(HOST_TARGET, src):
         BUILD.mkdir(exist_ok=True)
-        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-I", str(CSRC), str(src), "-o", str(HOST_TARGET)])
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-I", str(CSRC), "-isystem", str(_cuda_home() / "include"),
+              str(src), "-o", str(HOST_TARGET)])
     return HOST_TARGET
 
 

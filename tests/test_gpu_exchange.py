@@ -317,6 +317,26 @@ def test_fused_exchange_combine_oproj(helix, cp, B, H, D, hidden):
         assert helix.check_status(ws, r, cp)["code"] == 0
 
 
+def test_debug_bounds_checks_pass_on_valid_calls(helix, monkeypatch):
+    """HELIX_A2A_DEBUG=1 also checks every message's source and destination span on the device; valid calls must
+    come through with a clean status and unchanged results (invalid strides are exercised on the host only)."""
+    from helix_a2a_b200.ops import reference_math as rm
+    monkeypatch.setenv("HELIX_A2A_DEBUG", "1")
+    for cp in (2, 4, 8):
+        ws = _ws(helix, cp)
+        o = torch.randn(cp, 9, cp, 128, device="cuda").bfloat16()
+        s = torch.randn(cp, 9, cp, 4, device="cuda")
+        ro, rs = _ops().alltoall_debug(o, s, ws, 0, cp, True, 0, 0)
+        assert torch.equal(ro, o.transpose(0, 2).contiguous()) and torch.equal(rs, s.transpose(0, 2).contiguous())
+        outs = torch.randn(cp, 6, 16 * cp, 128, device="cuda").bfloat16()
+        lses = torch.randn(cp, 6, 16 * cp, device="cuda")
+        got, glse = _ops().alltoall_combine(outs, lses, ws, 0, cp, 0, True, False, 0, True, 0, 0)
+        want, wl = rm.head_scatter_combine_reference(outs, lses, return_lse=True)
+        assert (got.float() - want).abs().max() < 2e-2 and (glse - wl).abs().max() < 1e-4
+        for r in range(cp):
+            assert helix.check_status(ws, r, cp)["code"] == 0
+
+
 def test_debug_mode_poison_and_nvtx(helix):
     """HELIX_A2A_DEBUG=1 pre-fills outputs with NaN and verifies every row was written; NVTX ranges are harmless."""
     cp = 2

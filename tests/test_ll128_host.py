@@ -204,3 +204,40 @@ def test_model_detects_deadlock_without_in_call_publish(lib):
 def test_model_dead_sender_is_detected(lib):
     rc, _ = _run_model(lib, 4, [8], 33, 2, drop=1)
     assert rc == 3
+
+
+def _violations(host_lib, cp, outer, inner, mode, o_bytes, st_words, lse_scalar, strides, extents, has_st=1):
+    import ctypes
+    f = host_lib.helix_bounds_violations
+    f.restype = ctypes.c_int
+    ll = ctypes.c_longlong
+    return f(cp, outer, inner, mode, o_bytes, st_words, lse_scalar, *[ll(x) for x in strides], *[ll(x) for x in extents],
+             has_st)
+
+
+def test_debug_bounds_checks_accept_the_bindings_strides_and_catch_wrong_ones(host_lib):
+    """The per-message span checks of the exchange's debug mode, walked on the host over whole launches."""
+    # combine mode, native layout: attn_out [B, H, D] bf16, lse [B, H] -> out [B, H/cp, D], global lse [B, H/cp]
+    B, H, cp, D = 5, 16, 4, 128
+    Hl = H // cp
+    strides = [H * D * 2, Hl * D * 2, D * 2, H * 4, Hl * 4, 4, D * 2, 0, 0, 0]
+    extents = [B * H * D * 2, B * H * 4, B * Hl * D * 2, B * Hl * 4]
+    assert _violations(host_lib, cp, B, Hl, 1, D * 2, 1, 1, strides, extents) == 0
+    bad = list(strides)
+    bad[1] = Hl * D * 2 + 16                      # peer stride too long: the last peers' rows leave the tensor
+    assert _violations(host_lib, cp, B, Hl, 1, D * 2, 1, 1, bad, extents) > 0
+    bad = list(strides)
+    bad[6] = D * 2 * 2                            # destination rows twice as far apart as the output is large
+    assert _violations(host_lib, cp, B, Hl, 1, D * 2, 1, 1, bad, extents) > 0
+    short = list(extents)
+    short[1] -= 4                                 # LSE tensor one float short
+    assert _violations(host_lib, cp, B, Hl, 1, D * 2, 1, 1, strides, short) == 1
+    # exchange mode, the reference's layout: partial_o [E, cp, D], stats [E, cp, S]
+    E, S = 7, 6
+    strides = [cp * D * 2, D * 2, 0, cp * S * 4, S * 4, 0, cp * D * 2, D * 2, cp * S * 4, S * 4]
+    extents = [E * cp * D * 2, E * cp * S * 4, E * cp * D * 2, E * cp * S * 4]
+    assert _violations(host_lib, cp, E, 1, 0, D * 2, S // 2, 0, strides, extents) == 0
+    extents[2] -= D * 2                           # output one row short: exactly the last (entry, peer) row is out
+    assert _violations(host_lib, cp, E, 1, 0, D * 2, S // 2, 0, strides, extents) == 1
+    # extents that were not recorded switch the check off
+    assert _violations(host_lib, cp, E, 1, 0, D * 2, S // 2, 0, strides, [0, 0, 0, 0]) == 0
