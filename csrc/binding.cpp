@@ -62,7 +62,26 @@ void check_workspace(const torch::Tensor& workspace, int64_t cp_size) {
   TORCH_CHECK(workspace.size(1) * 8 >= need, "workspace rows are too small: ", workspace.size(1) * 8, " < ", need);
 }
 
+// device timeline of the exchange kernel (HELIX_A2A_EXCHANGE_TRACE=1): one buffer per device, overwritten by every call
+std::map<int, torch::Tensor> g_exchange_trace;
+constexpr int64_t kTraceWords = (int64_t)helix::kMaxEmulatedRanks * 256 * 8;
+
+unsigned long long* exchange_trace_buffer(const torch::Device& dev) {
+  static const bool on = [] { const char* v = std::getenv("HELIX_A2A_EXCHANGE_TRACE"); return v && std::string(v) == "1"; }();
+  if (!on) return nullptr;
+  torch::Tensor& t = g_exchange_trace[dev.index()];
+  if (!t.defined()) t = torch::zeros({kTraceWords}, torch::TensorOptions().dtype(torch::kInt64).device(dev));
+  return reinterpret_cast<unsigned long long*>(t.data_ptr());
+}
+
+torch::Tensor exchange_trace(torch::Tensor like) {
+  auto it = g_exchange_trace.find(like.device().index());
+  TORCH_CHECK(it != g_exchange_trace.end() && it->second.defined(), "no exchange trace: set HELIX_A2A_EXCHANGE_TRACE=1");
+  return it->second.clone().view({-1, 8});
+}
+
 void fill_workspace(helix::ExchangeParams& p, const torch::Tensor& workspace) {
+  p.trace = exchange_trace_buffer(workspace.device());
   p.workspace = reinterpret_cast<uint64_t*>(workspace.data_ptr());
   p.row_stride_bytes = workspace.stride(0) * 8;
   p.sm_count = helix::device_sm_count();
@@ -373,6 +392,7 @@ TORCH_LIBRARY(helix_a2a_b200, m) {
       "return_lse, bool base2, int stats_mode, bool emulate, int skip_peer_mask, int timeout_ms) -> (Tensor, Tensor)",
       &alltoall_combine);
   m.def("read_status(Tensor workspace, int cp_rank, int cp_size) -> Tensor", &read_status);
+  m.def("exchange_trace(Tensor like) -> Tensor", &exchange_trace);
   m.def("lse_combine(Tensor outputs, Tensor lses, int rank_dim, bool return_lse, bool base2) -> (Tensor, Tensor)",
         &lse_combine);
   register_compute_ops(m);

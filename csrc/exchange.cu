@@ -35,9 +35,14 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_kernel(const __grid_con
   const int rank = p.rank_base + blockIdx.y;
   const RankIO& io = p.io[blockIdx.y];
 
+  unsigned long long* tr = p.trace ? p.trace + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
   if (threadIdx.x == 0) {
     ctl.abort = 0;
     ctl.done = 0;
+    if (tr) {
+      tr[0] = globaltimer_ns();
+      for (int i = 1; i < 8; ++i) tr[i] = 0;
+    }
   }
   __syncthreads();
   // With programmatic dependent launch the inputs (the attention kernel's outputs) are only
@@ -46,6 +51,8 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_kernel(const __grid_con
   pdl_launch_dependents();
   Ctx cx = make_ctx(p, &ctl, rank, blockIdx.x);
   cx.deadline = globaltimer_ns() + p.timeout_ns;
+  cx.trace = tr;
+  if (tr && threadIdx.x == 0) tr[1] = globaltimer_ns();
   load_ring_heads(p, cx);
 
   if (warp < NS) {
@@ -54,6 +61,10 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_kernel(const __grid_con
     receiver_combine_warp<BF16, NIT>(p, cx, io, warp - NS, NR, lane, reinterpret_cast<float*>(dyn_smem), NoHook());
   } else {
     receiver_exchange_warp<NIT>(p, cx, io, warp - NS, NR, lane);
+  }
+  if (tr) {
+    __syncthreads();
+    if (threadIdx.x == 0) tr[6] = globaltimer_ns();
   }
 }
 

@@ -62,6 +62,10 @@ struct ExchangeParams {
   int recv_warps;       // receiver warps per CTA
   int group_warps;      // combine: receiver warps that share one entry (each polls a subset of peers)
   int rounds_per_publish;  // 0: publish consumed counts only at the end of the call
+  // Optional device timeline (HELIX_A2A_EXCHANGE_TRACE=1): [ranks_in_launch][channels][8] %globaltimer stamps per
+  // CTA: kernel entry, after the wait on the previous kernel, first line posted, last line posted, first message
+  // complete, last message complete, exit (0: the CTA never got there).  null: no tracing.
+  unsigned long long* trace;
   // debug bounds checks (bounds.cuh): byte extents of one rank's tensors, 0 = not recorded
   int64_t o_src_bytes, st_src_bytes, o_dst_bytes, st_dst_bytes;
   int debug_checks;         // check every message's source / destination span against the extents

@@ -75,6 +75,7 @@ struct Control {
 };
 
 struct Ctx {
+  unsigned long long* trace;   // this CTA's eight time stamps, or null
   uint8_t* ws;
   int64_t stride;
   uint8_t* my_row;
@@ -315,6 +316,7 @@ HELIX_D void sender_warp(const ExchangeParams& p, const Ctx& cx, const RankIO& i
       for (int i = k; i < n_mine && ok; i += K) ok = check_source(p, cx, c + i * C, peer, lane);
       if (!ok) continue;                       // reported; nothing is read or sent for this peer
     }
+    if (cx.trace != nullptr && send_warp == 0 && lane == 0 && cx.trace[2] == 0) cx.trace[2] = globaltimer_ns();
     uint64_t lo[NIT], hi[NIT];
     if (single_slab && k < n_mine) load_message<NIT>(p, msg_src(p, io, c + k * C, peer), 0, nchunks, payload_words, lane, lo, hi);
     for (int i = k; i < n_mine && ok; i += K) {
@@ -367,6 +369,7 @@ HELIX_D void sender_warp(const ExchangeParams& p, const Ctx& cx, const RankIO& i
     }
     // the line count of the call is fixed by its shape, so one warp per peer records it
     if (ok && k == 0 && lane == 0) st_volatile_8(sinfo + kSinfoHeadOff, head + (uint64_t)n_mine * L);
+    if (cx.trace != nullptr && send_warp == 0 && lane == 0) cx.trace[3] = globaltimer_ns();
   }
 }
 
@@ -513,6 +516,11 @@ HELIX_D void receiver_combine_warp(const ExchangeParams& p, const Ctx& cx, const
         }
         float l = ingest_lse(__shfl_sync(kFull, lo[0], 0), p.stats_mode, p.base2);
         acc.template add<BF16>(l, lo, hi);
+        if (cx.trace != nullptr && r == 0 && lane == 0) {
+          const unsigned long long now = globaltimer_ns();
+          if (cx.trace[4] == 0) cx.trace[4] = now;
+          cx.trace[5] = now;
+        }
       }
     }
     if (G > 1) {
@@ -594,6 +602,7 @@ HELIX_D Ctx make_ctx(const ExchangeParams& p, Control* ctl, int rank, int channe
   cx.rank = rank;
   cx.channel = channel;
   cx.deadline = 0;
+  cx.trace = nullptr;
   return cx;
 }
 

@@ -20,6 +20,7 @@ from .api import (
     allocate_workspace,
     check_status,
     debug_info,
+    exchange_trace,
     init_workspace,
     init_workspace_all_rows,
     lse_combine,
@@ -38,6 +39,7 @@ __all__ = [
     "check_status",
     "reset_workspace",
     "debug_info",
+    "exchange_trace",
     "init_workspace_all_rows",
     "HelixTimeoutError",
     "__version__",

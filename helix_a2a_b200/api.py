@@ -236,6 +236,15 @@ def check_status(workspace: torch.Tensor, cp_rank: int, cp_size: int, *, raise_o
     return info
 
 
+def exchange_trace(workspace: torch.Tensor) -> torch.Tensor:
+    """Device timeline of the LAST exchange launch on the workspace's device (needs ``HELIX_A2A_EXCHANGE_TRACE=1`` set
+    before the first call): an ``[n, 8]`` int64 tensor of ``%globaltimer`` stamps, one row per CTA (= channel) in
+    launch order: kernel entry, after the wait on the previous kernel, first line posted, last line posted, first
+    peer message complete, last peer message complete, exit, unused.  Rows of CTAs that were not launched are zero."""
+    from .ops._ext import ops
+    return ops().exchange_trace(workspace)
+
+
 def debug_info(workspace: Optional[torch.Tensor] = None) -> dict:
     """Launch shape chosen by the auto-tuner for the last call, and the workspace kind."""
     from .ops._ext import ext

@@ -24,6 +24,7 @@ EXTENSION_KNOBS = {
     "HELIX_A2A_DEBUG": ("0", "1: exchange outputs are pre-filled with NaN so that an unwritten row shows"),
     "HELIX_A2A_OPROJ_STREAMK": ("unset", "1 / 0: force / forbid the stream-K o_proj kernel where the library would choose"),
     "HELIX_A2A_OPROJ_TRACE": ("0", "1: the stream-K o_proj kernel records %globaltimer stamps per CTA"),
+    "HELIX_A2A_EXCHANGE_TRACE": ("0", "1: the exchange kernel records per-channel %globaltimer stamps (api.exchange_trace)"),
     "HELIX_A2A_ATTN_TRACE": ("0", "1: the GQA decode kernel records per-CTA %globaltimer stamps, SM id and chunk counts"),
     "HELIX_A2A_ATTN_DYN_PCT": ("unset", "percent of every long (sequence, kv head) pair handed out dynamically; 0: fixed shares"),
     "HELIX_A2A_ATTN_DYN_CHUNK": ("unset", "blocks of 16 tokens per dynamically drawn chunk"),
