@@ -5,6 +5,9 @@
     python benchmarks/profile_case.py oproj     # o_proj, 8 tokens, K=8192, hidden 8192 (134 MB of W)
     python benchmarks/profile_case.py exchange  # fused exchange+combine, 4 ranks played by one launch
     python benchmarks/profile_case.py mla       # MLA fp8 decode, B=8, 16K tokens per sequence
+    python benchmarks/profile_case.py fused     # one-kernel exchange+combine+o_proj, 8 ranks played by one launch
+    python benchmarks/profile_case.py streamk   # stream-K o_proj, 8 tokens, K=8192, hidden 8192
+    python benchmarks/profile_case.py combine   # stand-alone LSE combine, 8 ranks x 4096 rows x 512
 """
 import os
 import sys
@@ -34,6 +37,29 @@ def main():
         x = torch.randn(8, 8192, device="cuda").bfloat16()
         for _ in range(launches):
             oproj(x, w)
+    elif which == "streamk":
+        from helix_a2a_b200.ops.oproj import oproj
+        w = (torch.randn(8192, 8192, device="cuda") * 0.02).bfloat16()
+        x = torch.randn(8, 8192, device="cuda").bfloat16()
+        for _ in range(launches):
+            oproj(x, w, splits=-1)
+    elif which == "combine":
+        import helix_a2a_b200 as helix
+        o = torch.randn(8, 32, 128, 512, device="cuda").bfloat16()
+        l = torch.randn(8, 32, 128, device="cuda")
+        for _ in range(launches):
+            helix.lse_combine(o, l)
+    elif which == "fused":
+        import helix_a2a_b200 as helix
+        from helix_a2a_b200.ops._ext import ops
+        cp, B, H, D, hidden = 8, 8, 64, 128, 1024      # per rank: K = 1024 in two head groups, 8 slabs
+        ws = helix.allocate_workspace(cp, 0)
+        helix.init_workspace_all_rows(ws, cp)
+        outs = torch.randn(cp, B, H, D, device="cuda").bfloat16()
+        lses = torch.randn(cp, B, H, device="cuda")
+        w = (torch.randn(cp, hidden, (H // cp) * D, device="cuda") * 0.05).bfloat16()
+        for _ in range(launches):
+            ops().alltoall_combine_oproj(outs, lses, w, ws, 0, cp, False, True, 0)
     elif which == "mla":
         import math
         from helix_a2a_b200.ops import attention, reference_math as rm

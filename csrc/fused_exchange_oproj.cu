@@ -35,12 +35,16 @@ using namespace dev;
 using namespace sm100;
 
 constexpr int kReadersDoneOff = 64;   // byte offset inside the status block of the local row
-constexpr int kGemmThreads = 128;
+constexpr int kGemmThreads = 128;     // warps 0..3: weight requests, UMMA issue, epilogue
+constexpr int kRecvThreads = 512;     // all sixteen warps of a GEMM CTA receive and combine
 constexpr int kGemmBarrier = 2;       // named barrier of the 128 GEMM threads
+constexpr int kRecvBarrier = 3;       // named barrier of all 512 threads of a GEMM CTA
+constexpr int kMaxSources = 8;        // this rank + at most 7 peers per entry (cp <= 8)
 constexpr int kMaxAtoms = 8;          // K-slice of a GEMM CTA: at most 8 atoms of 64 = 512
 constexpr int kMaxRt0 = kMaxCp * 32;  // consumed-line counts cached per CTA: peers x channels
 
 __device__ __forceinline__ void gemm_sync() { named_barrier(kGemmBarrier, kGemmThreads); }
+__device__ __forceinline__ void recv_sync() { named_barrier(kRecvBarrier, kRecvThreads); }
 
 template <bool BF16, int NIT>
 __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __grid_constant__ FusedParams fp) {
@@ -75,7 +79,6 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   }
 
   // --------------------------------------------------------------------------------- GEMM role
-  if (tid >= kGemmThreads) return;
   const OprojParams& gp = fp.gemm[blockIdx.y];
   const int gidx = (int)blockIdx.x - fp.exchange_ctas;
   const int m_tile = gidx / gp.splits, split = gidx % gp.splits;
@@ -104,7 +107,7 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
     tmem_relinquish();
   }
   tc_fence_before_sync();
-  gemm_sync();
+  recv_sync();
   tc_fence_after_sync();
   const uint32_t tmem_d = tmem_slot;
 
@@ -128,11 +131,11 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   const unsigned long long deadline = cx.deadline;
 
   // consumed-line count of every ring of this row at the start of the call
-  for (int idx = tid; idx < N * C; idx += kGemmThreads) {
+  for (int idx = tid; idx < N * C; idx += kRecvThreads) {
     const int peer = idx / C, c = idx - peer * C;
     s_rt0[idx] = peer != rank ? ld_volatile_8(cx.my_row + rinfo_slot(cx.lay, peer, c) + kRinfoTailOff) : 0ull;
   }
-  gemm_sync();
+  recv_sync();
 
   // ---- receive + combine: the rows of this CTA's head group, straight into the B operand ----------------
   const int payload_words = p.st_words + (p.o_bytes >> 3);
@@ -140,36 +143,67 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   const int nchunks = L * kChunksPerLine;
   const int Hl = p.inner;
   bool alive = true;
-  for (int ent = warp; ent < p.outer * Hg && alive; ent += kGemmThreads / 32) {
+  for (int ent = warp; ent < p.outer * Hg && alive; ent += kRecvThreads / 32) {
     const int b = ent / Hg, hg = ent - b * Hg;
     const int hl = split * Hg + hg;
     const int e = b * Hl + hl;
     const int c = e % C, i = e / C;
     cx.channel = c;
-    Acc<NIT> acc;
-    acc.init();
-    uint64_t lo[NIT], hi[NIT];
-    load_message<NIT>(p, msg_src(p, io, e, rank), 0, nchunks, payload_words, lane, lo, hi);
-    acc.template add<BF16>(ingest_lse(__shfl_sync(kFull, lo[0], 0), p.stats_mode, p.base2), lo, hi);
-    for (int j = 0; j < N - 1; ++j) {
-      const int peer = (rank + N - 1 - j) % N;
-      const uint64_t q0 = s_rt0[peer * C + c] + (uint64_t)i * L;
-      const uint8_t* ring = cx.my_row + ring_offset(cx.lay, peer, c);
-      if (!poll_message<NIT>(cx, ring, q0, 0, nchunks, lane, lo, hi)) {
-        if (lane == 0) report(cx, kTimeoutRecv, peer, e);
+    // All sources of the entry at once: this rank's own row and the message of every peer are requested together
+    // (one 16-byte chunk per lane and source: a message fits one warp-wide load), so an entry whose lines have
+    // landed costs one round trip to L2 however many ranks there are; only sources whose flags are not all there
+    // yet are read again.
+    uint64_t lo[kMaxSources], hi[kMaxSources];
+    {
+      uint64_t l1[1], h1[1];
+      load_message<1>(p, msg_src(p, io, e, rank), 0, nchunks, payload_words, lane, l1, h1);
+      lo[0] = l1[0];
+      hi[0] = h1[0];
+    }
+    unsigned pending = (1u << (N - 1)) - 1u;          // bit j: peer (rank + N - 1 - j) % N still incomplete
+    unsigned spins = 0;
+    while (pending != 0u) {
+#pragma unroll
+      for (int j = 0; j < kMaxSources - 1; ++j) {
+        if ((pending >> j) & 1u) {
+          const int peer = (rank + N - 1 - j) % N;
+          const uint64_t q0 = s_rt0[peer * C + c] + (uint64_t)i * L;
+          const uint8_t* ring = cx.my_row + ring_offset(cx.lay, peer, c);
+          lo[j + 1] = hi[j + 1] = 0ull;
+          if (lane < nchunks) ld_volatile_16(ring + ll128::chunk_ring_offset(q0, lane), lo[j + 1], hi[j + 1]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kMaxSources - 1; ++j) {
+        if ((pending >> j) & 1u) {
+          const int peer = (rank + N - 1 - j) % N;
+          const uint64_t q0 = s_rt0[peer * C + c] + (uint64_t)i * L;
+          const bool bad = lane < nchunks && (lane & 7) == 7 && hi[j + 1] != ll128::flag_of(q0 + (uint64_t)(lane >> 3));
+          if (!__any_sync(kFull, bad)) pending &= ~(1u << j);
+        }
+      }
+      if (pending != 0u && (++spins & 31u) == 0u && __any_sync(kFull, give_up(cx))) {
+        if (lane == 0) report(cx, kTimeoutRecv, (rank + N - 1 - (__ffs(pending) - 1)) % N, e);
         alive = false;
         break;
       }
-      acc.template add<BF16>(ingest_lse(__shfl_sync(kFull, lo[0], 0), p.stats_mode, p.base2), lo, hi);
     }
     if (!alive) break;
+    Acc<1> acc;
+    acc.init();
+#pragma unroll
+    for (int j = 0; j < kMaxSources; ++j) {
+      if (j < N) {
+        uint64_t l1[1] = {lo[j]}, h1[1] = {hi[j]};
+        acc.template add<BF16>(ingest_lse(__shfl_sync(kFull, lo[j], 0), p.stats_mode, p.base2), l1, h1);
+      }
+    }
     const float inv = acc.s > 0.f ? 1.0f / acc.s : 0.f;
     uint8_t* xg = (fp.x_out[blockIdx.y] != nullptr && m_tile == 0)
                       ? reinterpret_cast<uint8_t*>(fp.x_out[blockIdx.y]) + ((int64_t)b * Hl + hl) * p.o_bytes
                       : nullptr;
-#pragma unroll
-    for (int it = 0; it < NIT; ++it) {
-      const int ch = it * 32 + lane;
+    {
+      const int it = 0, ch = lane;
       if (ch < nchunks) {
         const ll128::ChunkMap m = ll128::chunk_map(ch);
         float f[8];
@@ -193,8 +227,9 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   }
   // rows written by ordinary stores must be visible to the tensor core's (asynchronous-proxy) reads
   fence_proxy_async_smem();
-  gemm_sync();
+  recv_sync();
   const bool bad = *reinterpret_cast<volatile int*>(&ctl.abort) != 0;
+  if (tid >= kGemmThreads) return;        // the receive-only warps are done
 
   // this CTA has read its last line: count it out; the last one of the call publishes the consumed counts
   if (warp == 0) {
@@ -345,15 +380,17 @@ cudaError_t launch_exchange_oproj(FusedParams fp, int channel_override, bool pdl
   fp.heads_per_split = Hg;
 
   LaunchInfo li = plan_launch(p, channel_override);
-  FusedFn fn = nullptr;
-  if (li.iters <= 1) fn = pick<1>(p.is_bf16);
-  else if (li.iters <= 2) fn = pick<2>(p.is_bf16);
-  else if (li.iters <= 3) fn = pick<3>(p.is_bf16);
-  else if (li.iters <= 5) fn = pick<5>(p.is_bf16);
-  else return cudaErrorNotSupported;
+  // a message must fit one warp-wide load (at most 4 lines: heads of up to 232 dims) and an entry has at most 8 sources
+  if (li.iters > 1 || p.cp_size > kMaxSources) return cudaErrorNotSupported;
+  FusedFn fn = pick<1>(p.is_bf16);
 
   const int gemm_ctas = g0.hidden / 128 * g0.splits;
-  const int threads = std::max(32 * li.send_warps, kGemmThreads);
+  // few sender CTAs share all entries of the call: every warp of a sender CTA sends (as many per peer as fit)
+  {
+    const int peers = std::max(1, p.cp_size - 1), warps = kRecvThreads / 32;
+    li.send_warps = peers * std::max(1, warps / peers);
+  }
+  const int threads = kRecvThreads;
   const size_t smem = fused_smem_bytes(Kc, g0.n_pad);
   cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
