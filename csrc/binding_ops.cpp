@@ -425,6 +425,14 @@ std::tuple<torch::Tensor, torch::Tensor> fused_impl(torch::Tensor attn_out, torc
 
   helix::FusedParams fp{};
   helix::ExchangeParams& p = fp.ex;
+  {
+    // per-CTA %globaltimer stamps of the one-kernel path (read back with attn_trace)
+    static const bool trace_on = [] { const char* v = std::getenv("HELIX_A2A_EXCHANGE_TRACE"); return v && std::string(v) == "1"; }();
+    if (trace_on) {
+      if (!sc.trace.defined()) sc.trace = torch::zeros({helix::kGqaMaxCtas * 8}, attn_out.options().dtype(torch::kInt64));
+      p.trace = reinterpret_cast<unsigned long long*>(sc.trace.data_ptr());
+    }
+  }
   for (int r = 0; r < ranks; ++r) {
     p.io[r].o_src = reinterpret_cast<const uint8_t*>(attn_out.data_ptr()) + (int64_t)r * B * H * D * 2;
     p.io[r].st_src = reinterpret_cast<const uint8_t*>(lse.data_ptr()) + (int64_t)r * B * H * 4;

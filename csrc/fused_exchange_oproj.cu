@@ -61,6 +61,13 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   const RankIO& io = p.io[blockIdx.y];
   const int N = p.cp_size, C = p.channels;
 
+  // optional timeline: 8 words per CTA (entry, inputs ready, first / last line posted or receive done / accumulator
+  // ready, -, exit, role)
+  unsigned long long* tr = p.trace ? p.trace + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
+  if (tr && tid == 0) {
+    tr[0] = globaltimer_ns();
+    for (int i = 1; i < 8; ++i) tr[i] = 0;
+  }
   if ((int)blockIdx.x < fp.exchange_ctas) {
     // ------------------------------------------------------------------------------- send role
     if (tid == 0) {
@@ -72,9 +79,18 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
     pdl_launch_dependents();
     Ctx cx = make_ctx(p, &ctl, rank, blockIdx.x);
     cx.deadline = globaltimer_ns() + p.timeout_ns;
+    cx.trace = tr;
+    if (tr && tid == 0) tr[1] = globaltimer_ns();
     load_ring_heads(p, cx);
     const int NS = fp.send_warps;
     if (warp < NS) sender_warp<NIT>(p, cx, io, warp, NS, lane);
+    if (tr) {
+      __syncthreads();
+      if (tid == 0) {
+        tr[6] = globaltimer_ns();
+        tr[7] = 1;
+      }
+    }
     return;
   }
 
@@ -129,6 +145,7 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   Ctx cx = make_ctx(p, &ctl, rank, 0);
   cx.deadline = globaltimer_ns() + p.timeout_ns;
   const unsigned long long deadline = cx.deadline;
+  if (tr && tid == 0) tr[1] = globaltimer_ns();
 
   // consumed-line count of every ring of this row at the start of the call
   for (int idx = tid; idx < N * C; idx += kRecvThreads) {
@@ -228,6 +245,7 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   // rows written by ordinary stores must be visible to the tensor core's (asynchronous-proxy) reads
   fence_proxy_async_smem();
   recv_sync();
+  if (tr && tid == 0) tr[2] = globaltimer_ns();
   const bool bad = *reinterpret_cast<volatile int*>(&ctl.abort) != 0;
   if (tid >= kGemmThreads) return;        // the receive-only warps are done
 
@@ -293,6 +311,7 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
     if (!ok && lane == 0) atomicCAS(gp.error_flag, 0, (int)kTimeoutMbarrier);
   }
   tc_fence_after_sync();
+  if (tr && tid == 0) tr[3] = globaltimer_ns();
   const int row = warp * 32 + lane;
   const int hcol = m_tile * 128 + row;
   float* part = gp.splits > 1 ? gp.partial + ((size_t)(m_tile * gp.splits + split) * n_pad) * 128 : nullptr;
@@ -320,6 +339,10 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
     if (tid == 0) mbar_wait(&w_bar, 0, now_ns() + 2000000ull);
     return;
   }
+  if (tr && tid == 0) {
+    tr[6] = globaltimer_ns();       // without the fold of the K splits, which only the slab's last CTA runs
+    tr[7] = 2;
+  }
   if (gp.splits == 1) return;
 
   // ---- the head groups of a slab are K splits: the last CTA of the slab sums them -------------------------
@@ -344,6 +367,7 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
       if (tok0 + j < gp.tokens) gp.y[(int64_t)(tok0 + j) * gp.y_stride + m_tile * 128 + tid] = __float2bfloat16(accs[j]);
   }
   if (tid == 0) gp.counters[m_tile] = 0;
+  if (tr && tid == 0) tr[4] = globaltimer_ns();       // fold done
 }
 
 using FusedFn = void (*)(FusedParams);
