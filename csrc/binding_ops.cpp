@@ -417,11 +417,14 @@ std::tuple<torch::Tensor, torch::Tensor> fused_impl(torch::Tensor attn_out, torc
   auto stream = at::cuda::getCurrentCUDAStream();
   std::vector<int64_t> xs{B, K}, ys{B, hidden};
   if (emulate) { xs.insert(xs.begin(), cp_size); ys.insert(ys.begin(), cp_size); }
-  torch::Tensor x = emulate ? torch::empty(xs, attn_out.options()) : torch::empty({0}, attn_out.options());
+  // the combined activation exists in global memory for the tests (emulation) and when the slabs of a head group
+  // share its rows
+  const bool want_x = emulate || helix::fused_shares_rows((int)B, (int)(Hl / splits), (int)hidden);
+  torch::Tensor x = want_x ? torch::empty(xs, attn_out.options()) : torch::empty({0}, attn_out.options());
   torch::Tensor y = torch::empty(ys, attn_out.options());
   const int n_pad = (int)((B + 15) / 16 * 16);
   const int64_t part_floats = splits > 1 ? (int64_t)helix::oproj_partial_bytes((int)hidden, splits, n_pad) / 4 * ranks : 0;
-  Scratch& sc = scratch_for(attn_out.device(), hidden / 128 * ranks + 1024, part_floats, 0);
+  Scratch& sc = scratch_for(attn_out.device(), (hidden / 128 + helix::fused_aux_ints((int)hidden)) * ranks + 1024, part_floats, 0);
 
   helix::FusedParams fp{};
   helix::ExchangeParams& p = fp.ex;
@@ -438,7 +441,7 @@ std::tuple<torch::Tensor, torch::Tensor> fused_impl(torch::Tensor attn_out, torc
     p.io[r].st_src = reinterpret_cast<const uint8_t*>(lse.data_ptr()) + (int64_t)r * B * H * 4;
     p.io[r].o_dst = nullptr;
     p.io[r].st_dst = nullptr;
-    fp.x_out[r] = emulate ? reinterpret_cast<__nv_bfloat16*>(x.data_ptr()) + (int64_t)r * B * K : nullptr;
+    fp.x_out[r] = want_x ? reinterpret_cast<__nv_bfloat16*>(x.data_ptr()) + (int64_t)r * B * K : nullptr;
     helix::OprojParams& g = fp.gemm[r];
     if (w != nullptr) {
       torch::Tensor wr = emulate ? (*w)[r] : *w;
@@ -452,7 +455,12 @@ std::tuple<torch::Tensor, torch::Tensor> fused_impl(torch::Tensor attn_out, torc
     g.y_stride = hidden;
     // every emulated rank needs its own split partials and slab counters
     g.partial = splits > 1 ? sc.part_a.data_ptr<float>() + (int64_t)r * (part_floats / ranks) : nullptr;
-    g.counters = sc.counters.data_ptr<int32_t>() + (sc.counters.numel() - (hidden / 128) * (r + 1));
+    {
+      // from the end of the counter buffer: [slab counters | aux] per rank, all zero between calls
+      const int64_t per_rank = hidden / 128 + helix::fused_aux_ints((int)hidden);
+      g.counters = sc.counters.data_ptr<int32_t>() + (sc.counters.numel() - per_rank * (r + 1));
+      fp.aux[r] = g.counters + hidden / 128;
+    }
     g.error_flag = sc.error_flag.data_ptr<int32_t>();
     g.tokens = (int)B; g.n_pad = n_pad; g.hidden = (int)hidden; g.K = (int)K; g.splits = splits;
     g.timeout_ns = timeout_ms > 0 ? (unsigned long long)timeout_ms * 1000000ull : env_timeout_ns();

@@ -499,21 +499,17 @@ HELIX_D void receiver_combine_warp(const ExchangeParams& p, const Ctx& cx, const
     if (have && alive && (!check_source(p, cx, e, rank, lane) || !check_dest(p, cx, io, e, 0, lane))) alive = false;
     if (have && alive) {
       uint64_t lo[NIT], hi[NIT];
-      // This rank's own contribution comes straight from its attention output.  Its loads are only consumed after
-      // the first peer's message has been polled, so the two round trips to memory overlap.
-      uint64_t own_lo[NIT], own_hi[NIT];
-      bool own_pending = k == 0;
-      if (own_pending) load_message<NIT>(p, msg_src(p, io, e, rank), 0, nchunks, payload_words, lane, own_lo, own_hi);
+      if (k == 0) {  // this rank's own contribution comes straight from its attention output
+        const MsgSrc self = msg_src(p, io, e, rank);
+        load_message<NIT>(p, self, 0, nchunks, payload_words, lane, lo, hi);
+        float l = ingest_lse(__shfl_sync(kFull, lo[0], 0), p.stats_mode, p.base2);
+        acc.template add<BF16>(l, lo, hi);
+      }
       for (int j = k; j < N - 1; j += G) {
         const int peer = (rank + N - 1 - j) % N;
         const uint64_t q0 = __shfl_sync(kFull, rtail0, peer) + (uint64_t)i * L;
         const uint8_t* ring = cx.my_row + ring_offset(cx.lay, peer, c);
-        const bool got = poll_message<NIT>(cx, ring, q0, 0, nchunks, lane, lo, hi);
-        if (own_pending) {
-          acc.template add<BF16>(ingest_lse(__shfl_sync(kFull, own_lo[0], 0), p.stats_mode, p.base2), own_lo, own_hi);
-          own_pending = false;
-        }
-        if (!got) {
+        if (!poll_message<NIT>(cx, ring, q0, 0, nchunks, lane, lo, hi)) {
           if (lane == 0) report(cx, kTimeoutRecv, peer, e);
           alive = false;
           break;
@@ -526,8 +522,6 @@ HELIX_D void receiver_combine_warp(const ExchangeParams& p, const Ctx& cx, const
           cx.trace[5] = now;
         }
       }
-      if (own_pending)      // no peer polled (a single rank)
-        acc.template add<BF16>(ingest_lse(__shfl_sync(kFull, own_lo[0], 0), p.stats_mode, p.base2), own_lo, own_hi);
     }
     if (G > 1) {
       // park partial accumulators of warps 1..G-1, double-buffered by round parity

@@ -19,7 +19,23 @@ struct FusedParams {
   int gemm_ctas;                     // hidden / 128 * splits
   int send_warps;                    // sender warps of a sending CTA
   int heads_per_split;
+  // Rows shared between the slabs of a head group (set by the launcher when a call has many rows): the hidden / 128
+  // CTAs of a group each receive and combine 1 / (hidden / 128) of the group's rows, store them in x_out (then
+  // required), count them in aux and copy the complete group from L2 into their operand buffer.  0: every CTA
+  // receives all rows of its group itself (least latency for a few rows).
+  int share_rows;
+  // Per rank, zero on entry and on exit: [0, hidden / 128) second fold counter, then kFusedMaxGroups "rows ready"
+  // and kFusedMaxGroups "slabs done" counters (one per head group).
+  int* aux[kFusedMaxRanks];
 };
+
+constexpr int kFusedMaxGroups = 64;
+inline int fused_aux_ints(int hidden) { return hidden / 128 + 2 * kFusedMaxGroups; }
+// rows (token, head) a GEMM CTA would receive by itself above which the slabs of a group share them
+constexpr int kFusedShareAbove = 32;
+inline bool fused_shares_rows(int tokens, int heads_per_split, int hidden) {
+  return hidden / 128 > 1 && tokens * heads_per_split > kFusedShareAbove;
+}
 
 // Head groups for a rank that combines `heads_local` heads of `head_dim`: the fewest equal groups whose K-slice is
 // at most 512 wide; 0 when even one head is too wide (the fused kernel then does not apply).

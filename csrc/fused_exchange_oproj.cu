@@ -1,6 +1,7 @@
 // Helix exchange + LSE combine + o_proj in ONE kernel (sm_100a).
 //
-// The combined activation never exists in global memory and no CTA waits for another CTA of its own GPU:
+// With a few rows per call the combined activation never exists in global memory and no CTA waits for another
+// CTA of its own GPU; with many rows the slabs of a head group share the receive work (last paragraph):
 //   * CTAs [0, S) only SEND: their warps read this rank's attention output in place, frame LL128 lines in
 //     registers and post them into the peers' rings over NVLink (plain stores), then leave.
 //   * Every other CTA is a GEMM CTA that owns one 128-row slab of W_o and one group of heads (a K-slice of
@@ -17,8 +18,13 @@
 //     itself out when it has read its last line, and the one that counts last publishes the consumed line
 //     counts of all rings of the call (locally, and by remote 8-byte stores to the senders).  A call uses a
 //     small fraction of a ring, so senders never wait for that.
-// Senders depend on ring space only (granted by an EARLIER call), receivers on other GPUs' senders only: the
-// CTAs of one GPU need not be resident together, except when one launch plays several ranks for the tests.
+// Senders depend on ring space only (granted by an EARLIER call), receivers on other GPUs' senders only.
+//   * Many rows (more than kFusedShareAbove per GEMM CTA): receiving every row in every slab's CTA would repeat the
+//     poll + combine hidden / 128 times, so the slabs of a head group split the group's rows between them, store
+//     their combined rows in a global buffer (it stays in L2), count them, wait for the group's count and copy
+//     the complete group into their operand buffer with plain 16-byte loads.  The split-K fold is shared the same
+//     way (every CTA of a slab sums a share of the tokens once all partials are counted).  These waits are among
+//     CTAs of one launch: the launcher only accepts grids that are resident at once.
 // Every wait is bounded (%globaltimer); on expiry the status block / error flag is set and the kernel
 // returns.  No TMA load uses cluster broadcast; peer memory is only ever written, never read.
 #include "fused.h"
@@ -160,7 +166,13 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   const int nchunks = L * kChunksPerLine;
   const int Hl = p.inner;
   bool alive = true;
-  for (int ent = warp; ent < p.outer * Hg && alive; ent += kRecvThreads / 32) {
+  const int M = gp.hidden / 128;
+  const bool share = fp.share_rows != 0;
+  const int total_ent = p.outer * Hg;
+  // sharing: slab m takes rows m * 16 + warp, + M * 16, ... of the group; otherwise every CTA takes them all
+  const int ent_first = share ? m_tile * (kRecvThreads / 32) + warp : warp;
+  const int ent_step = (share ? M : 1) * (kRecvThreads / 32);
+  for (int ent = ent_first; ent < total_ent && alive; ent += ent_step) {
     const int b = ent / Hg, hg = ent - b * Hg;
     const int hl = split * Hg + hg;
     const int e = b * Hl + hl;
@@ -216,7 +228,7 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
       }
     }
     const float inv = acc.s > 0.f ? 1.0f / acc.s : 0.f;
-    uint8_t* xg = (fp.x_out[blockIdx.y] != nullptr && m_tile == 0)
+    uint8_t* xg = (fp.x_out[blockIdx.y] != nullptr && (share || m_tile == 0))
                       ? reinterpret_cast<uint8_t*>(fp.x_out[blockIdx.y]) + ((int64_t)b * Hl + hl) * p.o_bytes
                       : nullptr;
     {
@@ -234,11 +246,42 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
           const int byte = hg * p.o_bytes + 8 * (w - p.st_words);       // inside the CTA's K-slice of row b
           const int atom = byte >> 7, inb = byte & 127;
           const uint32_t off = (uint32_t)atom * atom_b_bytes + swz128((uint32_t)b, (uint32_t)(inb >> 4)) + (inb & 15);
-          *reinterpret_cast<uint64_t*>(smem_x + off) = packed;
+          if (!share) *reinterpret_cast<uint64_t*>(smem_x + off) = packed;
           if (xg != nullptr) *reinterpret_cast<uint64_t*>(xg + 8 * (w - p.st_words)) = packed;
         };
         put(w0, f);
         if (!m.has_flag) put(w1, f + 4);
+      }
+    }
+  }
+  if (share) {
+    // hand the rows over: publish this CTA's share, wait for the whole group, copy it from L2 into the operand
+    __threadfence();
+    recv_sync();
+    int* ready = fp.aux[blockIdx.y] + M + split;
+    if (tid == 0) {
+      int mine = 0;
+      for (int e0 = m_tile * (kRecvThreads / 32); e0 < total_ent; e0 += ent_step) mine += min(kRecvThreads / 32, total_ent - e0);
+      atomicAdd(ready, mine);     // also after a failed wait: the call is reported as failed, the counters stay balanced
+      unsigned spins = 0;
+      while (*reinterpret_cast<volatile int*>(ready) < total_ent) {
+        if ((++spins & 63u) == 0u && (*reinterpret_cast<volatile int*>(&ctl.abort) || now_ns() > deadline)) {
+          atomicCAS(gp.error_flag, 0, (int)kTimeoutMbarrier);
+          *reinterpret_cast<volatile int*>(&ctl.abort) = 1;
+          break;
+        }
+      }
+      __threadfence();
+    }
+    recv_sync();
+    if (!*reinterpret_cast<volatile int*>(&ctl.abort)) {
+      const int cpr = Kc >> 3;                                      // 16-byte chunks per row of the K-slice
+      const size_t row_bytes = (size_t)Hl * p.o_bytes;
+      const uint8_t* xs = reinterpret_cast<const uint8_t*>(fp.x_out[blockIdx.y]) + (size_t)split * Kc * 2;
+      for (int idx = tid; idx < p.outer * cpr; idx += kRecvThreads) {
+        const int b = idx / cpr, ch = idx - b * cpr;
+        const int4 v = __ldcg(reinterpret_cast<const int4*>(xs + (size_t)b * row_bytes + (size_t)ch * 16));
+        *reinterpret_cast<int4*>(smem_x + (uint32_t)(ch >> 3) * atom_b_bytes + swz128((uint32_t)b, (uint32_t)(ch & 7))) = v;
       }
     }
   }
@@ -250,6 +293,15 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   if (tid >= kGemmThreads) return;        // the receive-only warps are done
 
   // this CTA has read its last line: count it out; the last one of the call publishes the consumed counts
+  if (share && tid == 0) {
+    // this slab has its copy of the group's rows; the last slab re-arms the group's counters for the next call
+    int* ready = fp.aux[blockIdx.y] + M + split;
+    int* done = ready + kFusedMaxGroups;
+    if (atomicAdd(done, 1) == M - 1) {
+      *reinterpret_cast<volatile int*>(ready) = 0;
+      *reinterpret_cast<volatile int*>(done) = 0;
+    }
+  }
   if (warp == 0) {
     unsigned int* readers = reinterpret_cast<unsigned int*>(cx.my_row + cx.lay.status_offset + kReadersDoneOff);
     int last = 0;
@@ -335,9 +387,9 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   gemm_sync();
   if (warp == 1) tmem_dealloc(tmem_d, tmem_cols);
   if (!ok) {
-    // the weight copies may still be on their way into this CTA's shared memory: give them a bounded moment
+    // the weight copies may still be on their way into this CTA's shared memory: give them a bounded moment.
+    // The CTA still takes part in the fold below (the call is reported as failed; the counters stay balanced).
     if (tid == 0) mbar_wait(&w_bar, 0, now_ns() + 2000000ull);
-    return;
   }
   if (tr && tid == 0) {
     tr[6] = globaltimer_ns();       // without the fold of the K splits, which only the slab's last CTA runs
@@ -345,9 +397,57 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   }
   if (gp.splits == 1) return;
 
-  // ---- the head groups of a slab are K splits: the last CTA of the slab sums them -------------------------
+  // ---- the head groups of a slab are K splits ---------------------------------------------------------------
   __threadfence();
   gemm_sync();
+  if (n_pad > 16) {
+    // many tokens: every CTA of the slab sums a share of the tokens once all partials are there (the CTAs of a
+    // launch are resident together, see the launcher)
+    if (tid == 0) {
+      atomicAdd(&gp.counters[m_tile], 1);
+      int good = 1;
+      unsigned spins = 0;
+      while (*reinterpret_cast<volatile int*>(&gp.counters[m_tile]) < gp.splits) {
+        if ((++spins & 63u) == 0u && now_ns() > deadline) {
+          atomicCAS(gp.error_flag, 0, (int)kTimeoutMbarrier);
+          good = 0;
+          break;
+        }
+      }
+      __threadfence();
+      s_last = good;
+    }
+    gemm_sync();
+    if (s_last) {
+      const int per = (gp.tokens + gp.splits - 1) / gp.splits;
+      const int t0 = split * per, t1 = min(gp.tokens, t0 + per);
+      const float* base = gp.partial + (size_t)m_tile * gp.splits * n_pad * 128;
+      for (int tok0 = t0; tok0 < t1; tok0 += 8) {
+        float accs[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) accs[j] = 0.f;
+        for (int s = 0; s < gp.splits; ++s) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (tok0 + j < t1) accs[j] += __ldcg(base + ((size_t)s * n_pad + tok0 + j) * 128 + tid);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (tok0 + j < t1) gp.y[(int64_t)(tok0 + j) * gp.y_stride + m_tile * 128 + tid] = __float2bfloat16(accs[j]);
+      }
+    }
+    gemm_sync();
+    if (tid == 0) {
+      int* fold_done = fp.aux[blockIdx.y] + m_tile;
+      if (atomicAdd(fold_done, 1) == gp.splits - 1) {
+        *reinterpret_cast<volatile int*>(&gp.counters[m_tile]) = 0;
+        *reinterpret_cast<volatile int*>(fold_done) = 0;
+      }
+      if (tr) tr[4] = globaltimer_ns();
+    }
+    return;
+  }
+  // few tokens: the last CTA of the slab sums them
   if (tid == 0) s_last = (atomicAdd(&gp.counters[m_tile], 1) == gp.splits - 1);
   gemm_sync();
   if (!s_last) return;
@@ -402,6 +502,12 @@ cudaError_t launch_exchange_oproj(FusedParams fp, int channel_override, bool pdl
   for (int r = 0; r < p.ranks_in_launch; ++r)
     if (fp.gemm[r].splits != g0.splits || (g0.splits > 1 && fp.gemm[r].partial == nullptr)) return cudaErrorInvalidValue;
   fp.heads_per_split = Hg;
+  fp.share_rows = fused_shares_rows(p.outer, Hg, g0.hidden) ? 1 : 0;
+  if (g0.splits > kFusedMaxGroups) return cudaErrorNotSupported;
+  for (int r = 0; r < p.ranks_in_launch; ++r) {
+    if (fp.aux[r] == nullptr) return cudaErrorInvalidValue;
+    if (fp.share_rows && fp.x_out[r] == nullptr) return cudaErrorInvalidValue;
+  }
 
   LaunchInfo li = plan_launch(p, channel_override);
   // a message must fit one warp-wide load (at most 4 lines: heads of up to 232 dims) and an entry has at most 8 sources
