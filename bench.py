@@ -82,9 +82,9 @@ def parse():
     ap.add_argument("--ctx", type=int, default=CTX)
     ap.add_argument("--batch-per-gpu", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--fuse-oproj", action="store_true",
-                    help="run exchange+combine+o_proj as ONE kernel (default: two kernels chained by PDL, which "
-                         "measured faster because each then has every SM to itself)")
+    ap.add_argument("--fuse-oproj", nargs="?", const="on", default="off", choices=["on", "off", "auto"],
+                    help="exchange+combine+o_proj as ONE kernel: on / auto = whenever the shape fits that kernel (for "
+                         "this model: cp = 8), off = two kernels chained by programmatic dependent launch")
     ap.add_argument("--no-pdl", action="store_true", help="do not chain the kernels by programmatic dependent launch")
     return ap.parse_args()
 
@@ -201,7 +201,7 @@ def run_helix(args):
     batch = args.batch_per_gpu * world
     local_ctx = args.ctx // world
     stack = HelixDecodeStack(cfg, batch=batch, local_ctx=local_ctx, cp_size=world, cp_rank=rank, group=cpu_group,
-                             fuse_oproj=args.fuse_oproj)
+                             fuse_oproj={"on": True, "off": False, "auto": None}[args.fuse_oproj])
     gen = torch.Generator().manual_seed(7)          # same q on every rank
     q_host = [torch.randn(cfg.n_layers, batch, cfg.n_q_heads, cfg.head_dim, generator=gen).bfloat16().pin_memory()
               for _ in range(2)]
@@ -283,11 +283,11 @@ def run_helix(args):
                        "hbm_bytes_per_step_per_gpu": kv_bytes + w_bytes,
                        "achieved_hbm_gbs": (kv_bytes + w_bytes) / (ms * 1e-3) / 1e9,
                        "path": {"attention": "helix gqa_decode (sm_100a, TMA + mbarrier)",
-                                "exchange": ("helix exchange+combine+o_proj in one kernel" if args.fuse_oproj
+                                "exchange": ("helix exchange+combine+o_proj in one kernel" if stack.fuse_oproj
                                              else "helix exchange+combine (one kernel)") if world > 1 else "none (cp=1)",
                                 "o_proj": "helix tcgen05 GEMM, weights " +
                                           ("packed once at load time (tile-major, pre-swizzled bf16; same values)"
-                                           if getattr(stack, "prepack_oproj", False) and not (world > 1 and args.fuse_oproj)
+                                           if getattr(stack, "prepack_oproj", False)
                                            else "plain [hidden, K]"),
                                 "pdl": os.environ.get("HELIX_A2A_ENABLE_PDL", "0") == "1"}},
         }

@@ -505,6 +505,10 @@ torch::Tensor alltoall_combine_oproj_packed(torch::Tensor attn_out, torch::Tenso
                                 timeout_ms));
 }
 
+bool fused_oproj_fits(int64_t tokens, int64_t heads_local, int64_t head_dim, int64_t hidden, int64_t cp_size) {
+  return helix::fused_fits((int)tokens, (int)heads_local, (int)head_dim, (int)hidden, (int)cp_size, helix::device_sm_count());
+}
+
 int64_t read_error_flag(torch::Tensor like) {
   Scratch& sc = scratch_for(like.device(), 1, 0, 0);
   return sc.error_flag.item<int>();
@@ -545,4 +549,5 @@ void register_compute_ops(torch::Library& m) {
 void bind_compute(pybind11::module_& m) {
   m.def("gqa_pick_ctas", &helix::gqa_pick_ctas);
   m.def("oproj_pick_splits", &helix::oproj_pick_splits);
+  m.def("fused_oproj_fits", &fused_oproj_fits);
 }

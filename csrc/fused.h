@@ -41,6 +41,9 @@ inline bool fused_shares_rows(int tokens, int heads_per_split, int hidden) {
 // at most 512 wide; 0 when even one head is too wide (the fused kernel then does not apply).
 int fused_pick_splits(int heads_local, int head_dim);
 size_t fused_smem_bytes(int k_slice, int n_pad);
+// The launcher's shape rules without a launch: would a call with these sizes run as one kernel on a device with
+// `sm_count` SMs (one CTA per SM)?  Callers use it to choose between the one-kernel path and the two-kernel chain.
+bool fused_fits(int tokens, int heads_local, int head_dim, int hidden, int cp_size, int sm_count);
 
 // Launches the fused kernel.  cudaErrorNotSupported: the shape does not fit (more than kFusedMaxTokens tokens, a
 // head wider than 512, more CTAs than the device holds at once, or a call that would fill half a ring); callers

@@ -488,6 +488,21 @@ int fused_pick_splits(int heads_local, int head_dim) {
 
 size_t fused_smem_bytes(int k_slice, int n_pad) { return (size_t)(k_slice / 64) * (128 + n_pad) * 128 + 1024; }
 
+bool fused_fits(int tokens, int heads_local, int head_dim, int hidden, int cp_size, int sm_count) {
+  if (tokens < 1 || cp_size < 2 || cp_size > kMaxSources || hidden % 128 != 0 || (head_dim * 2) % 128 != 0) return false;
+  const int splits = fused_pick_splits(heads_local, head_dim);
+  if (splits < 1 || splits > kFusedMaxGroups) return false;
+  const int n_pad = (tokens + 15) / 16 * 16, Kc = heads_local / splits * head_dim;
+  if (n_pad > kFusedMaxTokens || Kc % 64 != 0) return false;
+  const int L = ll128::lines_for_words(1 + head_dim / 4);
+  if (L > 4) return false;                                             // a message is one warp-wide load
+  if (fused_smem_bytes(Kc, n_pad) > 227 * 1024) return false;
+  const int gemm_ctas = hidden / 128 * splits, E = tokens * heads_local;
+  if (sm_count - gemm_ctas < 1) return false;                          // one CTA per SM, all resident at once
+  const int channels = std::max(1, std::min({E, sm_count - gemm_ctas, 32}));
+  return (int64_t)ceil_div(E, channels) * L <= kRingLines / 2;
+}
+
 cudaError_t launch_exchange_oproj(FusedParams fp, int channel_override, bool pdl, cudaStream_t stream,
                                   LaunchInfo* info_out) {
   ExchangeParams& p = fp.ex;

@@ -17,6 +17,7 @@ from .api import (
     alltoall,
     alltoall_combine,
     alltoall_combine_oproj,
+    alltoall_combine_oproj_fits,
     allocate_workspace,
     check_status,
     debug_info,
@@ -35,6 +36,7 @@ __all__ = [
     "alltoall",
     "alltoall_combine",
     "alltoall_combine_oproj",
+    "alltoall_combine_oproj_fits",
     "lse_combine",
     "check_status",
     "reset_workspace",

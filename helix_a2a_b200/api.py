@@ -196,6 +196,20 @@ def alltoall_combine_oproj(attn_out: torch.Tensor, lse: torch.Tensor, w_o, works
         return _oproj.oproj(x.reshape(B, -1), w_o)
 
 
+def alltoall_combine_oproj_fits(tokens: int, heads_local: int, head_dim: int, hidden: int, cp_size: int) -> bool:
+    """Would :func:`alltoall_combine_oproj` run as ONE kernel for these sizes on the current GPU?
+
+    ``heads_local`` = heads this rank combines (H / cp), ``hidden`` = rows of its o_proj weight.  The rules are the
+    launcher's (``csrc/fused_exchange_oproj.cu::fused_fits``): at most 64 tokens and 8 ranks, heads of at most 232
+    dims, head groups of at most 512 K-columns, and ``hidden / 128 x groups`` GEMM CTAs resident at once beside at
+    least one sender CTA.  False without the extension or a GPU.
+    """
+    from .ops import _ext
+    if not torch.cuda.is_available() or not _ext.available():
+        return False
+    return bool(_ext.ext().fused_oproj_fits(int(tokens), int(heads_local), int(head_dim), int(hidden), int(cp_size)))
+
+
 def lse_combine(outputs: torch.Tensor, lses: torch.Tensor, *, return_lse: bool = False, base2: bool = False,
                 layout: str = "NBHD"):
     """LSE-weighted combine of per-rank partial attention outputs that are already on this rank.

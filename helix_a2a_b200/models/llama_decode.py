@@ -52,13 +52,18 @@ class HelixDecodeStack:
 
     def __init__(self, cfg: LlamaDecodeConfig, *, batch: int, local_ctx: int, cp_size: int = 1, cp_rank: int = 0,
                  group: Optional[dist.ProcessGroup] = None, device="cuda", seed: int = 0,
-                 workspace: Optional[torch.Tensor] = None, kv_std: float = 1.0, fuse_oproj: bool = False):
+                 workspace: Optional[torch.Tensor] = None, kv_std: float = 1.0,
+                 fuse_oproj: Optional[bool] = False):
         assert cfg.n_q_heads % cp_size == 0, "query heads must divide evenly over the CP ranks"
         self.cfg, self.batch, self.local_ctx = cfg, batch, local_ctx
         self.cp_size, self.cp_rank, self.group = cp_size, cp_rank, group
-        self.fuse_oproj = fuse_oproj
         self.device = torch.device(device)
         self.heads_local = cfg.n_q_heads // cp_size
+        # exchange + combine + o_proj as one kernel: True / False, or None = whenever the shape fits that kernel
+        # (a request that does not fit runs the two-kernel chain, and is counted as such)
+        fits = cp_size > 1 and self.device.type == "cuda" and api.alltoall_combine_oproj_fits(
+            batch, self.heads_local, cfg.head_dim, cfg.hidden, cp_size)
+        self.fuse_oproj = bool(fits) if fuse_oproj is None else bool(fuse_oproj and fits)
         self.k_local = self.heads_local * cfg.head_dim
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         gen = torch.Generator(device=self.device)

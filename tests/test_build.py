@@ -36,3 +36,17 @@ def test_extension_builds(native_built):
     # MLA message: 1024 B row + 8 B stats -> 9 lines; GQA: 256 + 8 -> 3 lines
     assert C.wire_bytes(1032) == 9 * 128
     assert C.wire_bytes(264) == 3 * 128
+
+
+def test_one_kernel_path_shape_rules(native_built):
+    """The launcher's "does this shape run as one kernel" rules, as the model stacks query them (148 SMs)."""
+    from helix_a2a_b200.ops._ext import ext
+    fits = ext().fused_oproj_fits            # (tokens, heads per rank, head dim, hidden, cp)
+    assert fits(8, 8, 128, 8192, 8)          # Llama-3-70B at cp = 8: 64 slabs x 2 head groups = 128 GEMM CTAs
+    assert fits(64, 8, 128, 8192, 8)
+    assert not fits(65, 8, 128, 8192, 8)     # more than 64 tokens
+    assert not fits(8, 32, 128, 8192, 2)     # cp = 2: 64 slabs x 8 groups do not fit the device at once
+    assert fits(8, 32, 128, 2048, 2)
+    assert not fits(8, 16, 512, 7168, 8)     # MLA rows (512 dims) are 9 lines, more than one warp-wide load
+    assert not fits(8, 8, 128, 8192, 16)     # at most 8 ranks
+    assert not fits(8, 64, 128, 8192, 1)     # a single rank has nothing to exchange
