@@ -6,6 +6,7 @@
     python benchmarks/profile_case.py exchange  # fused exchange+combine, 4 ranks played by one launch
     python benchmarks/profile_case.py mla       # MLA fp8 decode, B=8, 16K tokens per sequence
     python benchmarks/profile_case.py fused     # one-kernel exchange+combine+o_proj, 8 ranks played by one launch
+    python benchmarks/profile_case.py fused_rows  # the same with 64 tokens (slabs of a head group share the rows)
     python benchmarks/profile_case.py streamk   # stream-K o_proj, 8 tokens, K=8192, hidden 8192
     python benchmarks/profile_case.py combine   # stand-alone LSE combine, 8 ranks x 4096 rows x 512
 """
@@ -49,10 +50,11 @@ def main():
         l = torch.randn(8, 32, 128, device="cuda")
         for _ in range(launches):
             helix.lse_combine(o, l)
-    elif which == "fused":
+    elif which in ("fused", "fused_rows"):
         import helix_a2a_b200 as helix
         from helix_a2a_b200.ops._ext import ops
-        cp, B, H, D, hidden = 8, 8, 64, 128, 1024      # per rank: K = 1024 in two head groups, 8 slabs
+        # per rank: K = 1024 in two head groups, 8 slabs; "fused_rows": 64 tokens, so the slabs share the rows
+        cp, B, H, D, hidden = 8, (8 if which == "fused" else 64), 64, 128, 1024
         ws = helix.allocate_workspace(cp, 0)
         helix.init_workspace_all_rows(ws, cp)
         outs = torch.randn(cp, B, H, D, device="cuda").bfloat16()
