@@ -40,6 +40,9 @@ unsigned long long timeout_ns(int64_t timeout_ms) {
   return (unsigned long long)ms * 1000000ull;
 }
 
+// what the auto-tuner chose for the most recent exchange launch of this process (debug_info); launches may come
+// from several threads (one per device), so reads and writes take the lock
+std::mutex g_last_launch_mu;
 helix::LaunchInfo g_last_launch{};
 
 // HELIX_A2A_DEBUG=1: outputs are pre-filled with NaN so that a row the kernel failed to write shows up
@@ -92,7 +95,10 @@ void launch(helix::ExchangeParams& p, int64_t timeout_ms) {
   auto stream = at::cuda::getCurrentCUDAStream();
   helix::LaunchInfo li{};
   check_cuda(helix::launch_exchange(p, env_channels(), env_pdl(), stream, &li), "exchange launch");
-  g_last_launch = li;
+  {
+    std::lock_guard<std::mutex> lk(g_last_launch_mu);
+    g_last_launch = li;
+  }
 }
 
 int64_t get_helix_workspace_size_per_rank(int64_t cp_size) {
@@ -472,14 +478,19 @@ PYBIND11_MODULE(_C, m) {
   m.def("close_fd", [](int fd) { return ::close(fd); });
 
   m.def("last_launch_info", []() {
+    helix::LaunchInfo li;
+    {
+      std::lock_guard<std::mutex> lk(g_last_launch_mu);
+      li = g_last_launch;
+    }
     py::dict d;
-    d["channels"] = g_last_launch.channels;
-    d["send_warps"] = g_last_launch.send_warps;
-    d["recv_warps"] = g_last_launch.recv_warps;
-    d["group_warps"] = g_last_launch.group_warps;
-    d["lines_per_message"] = g_last_launch.lines_per_message;
-    d["iters"] = g_last_launch.iters;
-    d["cooperative"] = g_last_launch.cooperative;
+    d["channels"] = li.channels;
+    d["send_warps"] = li.send_warps;
+    d["recv_warps"] = li.recv_warps;
+    d["group_warps"] = li.group_warps;
+    d["lines_per_message"] = li.lines_per_message;
+    d["iters"] = li.iters;
+    d["cooperative"] = li.cooperative;
     return d;
   });
   m.def("layout", [](int cp, int sm_count) {
