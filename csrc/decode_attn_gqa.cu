@@ -82,11 +82,6 @@ __device__ __forceinline__ int ld_relaxed(const int* p) {
   asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ int atom_add_release(int* p, int v) {
-  int prev;
-  asm volatile("atom.release.gpu.global.add.s32 %0, [%1], %2;" : "=r"(prev) : "l"(p), "r"(v) : "memory");
-  return prev;
-}
 __device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
   int prev;
   asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(prev) : "l"(p), "r"(v) : "memory");
@@ -595,10 +590,6 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
     if (nxt.valid) prologue(nxt);
 
     if (!nxt.valid || nxt.b != st_b || nxt.kvh != st_kvh) {
-      // Nothing left: this CTA draws and probes no more, so it is counted out of the pools NOW; the answer is only
-      // looked at after the merge and the fold below, whose time then hides the atomic's round trip.
-      int exit_prev = -1;
-      if (!nxt.valid && dyn_on && tid == 0) exit_prev = atom_add_release(exit_ctr, 1);
       // ---- leave the pair: merge the warps' partials, four heads per round --------------------------
       const bool whole = (st_blocks == st_nb);
       float* part_o = p.part_o + (size_t)st_slot * 8 * kD;
@@ -693,15 +684,6 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
           __syncthreads();                    // the list is read; the merge buffer may be reused
         }
       }
-      if (!nxt.valid && dyn_on && warp == 0) {
-        // the last CTA to leave re-arms the pools for the next launch: nobody draws or probes any more
-        const int last = __shfl_sync(0xffffffffu, exit_prev == G - 1 ? 1 : 0, 0);
-        if (last) {
-          __threadfence();                  // acquire side: every other CTA's last draw is behind its count
-          for (int i = lane; i < P; i += 32) pool_ctr[i] = 0;
-          if (lane == 0) *exit_ctr = 0;
-        }
-      }
       // the running state is consumed: a fresh one starts with the next segment
       st_active = false;
       m_run = -INFINITY;
@@ -724,14 +706,13 @@ __global__ void __launch_bounds__(kThreads, 2) gqa_decode_kernel(const __grid_co
         if ((++spins & 255u) == 0u && now_ns() > grace) break;
       }
     }
-  } else if (dyn_on && warp == 0 && it_ring == 0) {
-    // a CTA that never had a segment (more CTAs than work) is counted out here; every other CTA was counted in
-    // its last pass through the loop
+  } else if (dyn_on && warp == 0) {
+    // the last CTA to leave re-arms the pools for the next launch: nobody draws or probes any more (every warp
+    // of this CTA is past the loop above; only this warp waits for the atomic)
     int last = 0;
-    if (lane == 0) last = (atom_add_release(exit_ctr, 1) == G - 1);
+    if (lane == 0) last = (atom_add_acq_rel(exit_ctr, 1) == G - 1);
     last = __shfl_sync(0xffffffffu, last, 0);
     if (last) {
-      __threadfence();
       for (int i = lane; i < P; i += 32) pool_ctr[i] = 0;
       if (lane == 0) *exit_ctr = 0;
     }
