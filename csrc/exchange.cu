@@ -36,9 +36,8 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_kernel(const __grid_con
   const RankIO& io = p.io[blockIdx.y];
 
   unsigned long long* tr = p.trace ? p.trace + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
+  init_control(&ctl);
   if (threadIdx.x == 0) {
-    ctl.abort = 0;
-    ctl.done = 0;
     if (tr) {
       tr[0] = globaltimer_ns();
       for (int i = 1; i < 8; ++i) tr[i] = 0;
@@ -53,7 +52,6 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_kernel(const __grid_con
   cx.deadline = globaltimer_ns() + p.timeout_ns;
   cx.trace = tr;
   if (tr && threadIdx.x == 0) tr[1] = globaltimer_ns();
-  load_ring_heads(p, cx);
 
   if (warp < NS) {
     sender_warp<NIT>(p, cx, io, warp, NS, lane);

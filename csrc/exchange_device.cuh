@@ -69,10 +69,19 @@ HELIX_D void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_depen
 struct Control {
   int abort;
   unsigned done;
-  // Line count of every outgoing ring at kernel entry, read ONCE per CTA before the warps split into roles:
-  // several sender warps may share a ring, and the one that finishes first stores the new count.
-  unsigned long long head[kMaxCp];
+  // Sender warps that are done with the ring to a peer (several warps may share one ring: each reads the ring's
+  // line count when it starts, and the new count is only stored once all of them have counted themselves in here).
+  unsigned sent[kMaxCp];
 };
+
+// every thread of the CTA calls this before the first CTA barrier of the kernel
+HELIX_D void init_control(Control* ctl) {
+  if (threadIdx.x == 0) {
+    ctl->abort = 0;
+    ctl->done = 0;
+  }
+  if (threadIdx.x < kMaxCp) ctl->sent[threadIdx.x] = 0u;
+}
 
 struct Ctx {
   unsigned long long* trace;   // this CTA's eight time stamps, or null
@@ -309,16 +318,17 @@ HELIX_D void sender_warp(const ExchangeParams& p, const Ctx& cx, const RankIO& i
     if ((p.skip_peer_mask >> peer) & 1u) continue;
     uint8_t* ring = cx.ws + (int64_t)peer * cx.stride + ring_offset(cx.lay, rank, c);
     uint8_t* sinfo = cx.my_row + sinfo_slot(cx.lay, peer, c);
-    const uint64_t head = cx.ctl->head[peer];
+    // line count of the ring at kernel entry, consumed count, and the first message: one round trip for all three
+    const uint64_t head = ld_volatile_8(sinfo + kSinfoHeadOff);
     uint64_t tail = ld_volatile_8(sinfo + kSinfoTailOff);
     bool ok = true;
     if (p.debug_checks) {                      // debug: every message this warp is about to read must fit the tensors
       for (int i = k; i < n_mine && ok; i += K) ok = check_source(p, cx, c + i * C, peer, lane);
-      if (!ok) continue;                       // reported; nothing is read or sent for this peer
+      // not ok: reported; nothing is read or sent for this peer (the loops below are skipped)
     }
     if (cx.trace != nullptr && send_warp == 0 && lane == 0 && cx.trace[2] == 0) cx.trace[2] = globaltimer_ns();
     uint64_t lo[NIT], hi[NIT];
-    if (single_slab && k < n_mine) load_message<NIT>(p, msg_src(p, io, c + k * C, peer), 0, nchunks, payload_words, lane, lo, hi);
+    if (ok && single_slab && k < n_mine) load_message<NIT>(p, msg_src(p, io, c + k * C, peer), 0, nchunks, payload_words, lane, lo, hi);
     for (int i = k; i < n_mine && ok; i += K) {
       const int e = c + i * C;
       const uint64_t q0 = head + (uint64_t)i * L;
@@ -367,8 +377,23 @@ HELIX_D void sender_warp(const ExchangeParams& p, const Ctx& cx, const RankIO& i
         }
       }
     }
-    // the line count of the call is fixed by its shape, so one warp per peer records it
-    if (ok && k == 0 && lane == 0) st_volatile_8(sinfo + kSinfoHeadOff, head + (uint64_t)n_mine * L);
+    // The line count of the call is fixed by its shape, so one warp per ring records it, after every warp that shares
+    // the ring has read the old count (each counts itself in when it is done with the ring, whatever happened).
+    __syncwarp();
+    if (lane == 0) {
+      atomicAdd(&cx.ctl->sent[peer], 1u);
+      if (ok && k == 0) {
+        unsigned spins = 0;
+        bool all = true;
+        while (*reinterpret_cast<volatile unsigned*>(&cx.ctl->sent[peer]) < (unsigned)K) {
+          if ((++spins & 1023u) == 0u && give_up(cx)) {
+            all = false;
+            break;
+          }
+        }
+        if (all) st_volatile_8(sinfo + kSinfoHeadOff, head + (uint64_t)n_mine * L);
+      }
+    }
     if (cx.trace != nullptr && send_warp == 0 && lane == 0) cx.trace[3] = globaltimer_ns();
   }
 }
@@ -582,14 +607,6 @@ HELIX_D void receiver_combine_warp(const ExchangeParams& p, const Ctx& cx, const
     }
   }
   finish_receiver(p, cx, rtail0, n_mine, L, NR, lane);
-}
-
-// Fills ctl->head for the CTA's channel; every thread of the CTA must call it (it ends with a CTA barrier).
-HELIX_D void load_ring_heads(const ExchangeParams& p, const Ctx& cx) {
-  const int peer = (int)threadIdx.x;
-  if (peer < p.cp_size && peer != cx.rank)
-    cx.ctl->head[peer] = ld_volatile_8(cx.my_row + sinfo_slot(cx.lay, peer, cx.channel) + kSinfoHeadOff);
-  __syncthreads();
 }
 
 HELIX_D Ctx make_ctx(const ExchangeParams& p, Control* ctl, int rank, int channel) {

@@ -76,10 +76,7 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
   }
   if ((int)blockIdx.x < fp.exchange_ctas) {
     // ------------------------------------------------------------------------------- send role
-    if (tid == 0) {
-      ctl.abort = 0;
-      ctl.done = 0;
-    }
+    init_control(&ctl);
     __syncthreads();
     pdl_wait();
     pdl_launch_dependents();
@@ -87,7 +84,6 @@ __global__ void __launch_bounds__(512, 1) helix_exchange_oproj_kernel(const __gr
     cx.deadline = globaltimer_ns() + p.timeout_ns;
     cx.trace = tr;
     if (tr && tid == 0) tr[1] = globaltimer_ns();
-    load_ring_heads(p, cx);
     const int NS = fp.send_warps;
     if (warp < NS) sender_warp<NIT>(p, cx, io, warp, NS, lane);
     if (tr) {

@@ -20,6 +20,7 @@ from .api import (
     alltoall_combine_oproj_fits,
     allocate_workspace,
     check_status,
+    StatusPoller,
     debug_info,
     exchange_trace,
     init_workspace,
@@ -39,6 +40,7 @@ __all__ = [
     "alltoall_combine_oproj_fits",
     "lse_combine",
     "check_status",
+    "StatusPoller",
     "reset_workspace",
     "debug_info",
     "exchange_trace",

@@ -250,6 +250,44 @@ def check_status(workspace: torch.Tensor, cp_rank: int, cp_size: int, *, raise_o
     return info
 
 
+class StatusPoller:
+    """Watches the status block of the local row WITHOUT synchronising: every :meth:`poll` first looks at the copy
+    the previous poll requested (if it has arrived in pinned host memory) and then requests a fresh one on the
+    current stream (a 32-byte device-to-host copy and an event, no host wait).  A failure is therefore seen one or
+    two polls late, which is the price of not stalling a serving engine once per step; :func:`check_status` is the
+    blocking, immediate form.  Raises :class:`HelixTimeoutError` like it."""
+
+    def __init__(self, workspace: torch.Tensor, cp_rank: int, cp_size: int):
+        from .ops._ext import ext
+        self._cpu = isinstance(workspace, CpuWorkspace) or not workspace.is_cuda
+        if self._cpu:
+            return
+        off = int(ext().layout(int(cp_size), ws_mod._sm_count(workspace.device))["status_offset"])
+        assert off % 8 == 0
+        self._view = workspace[cp_rank, off // 8: off // 8 + 4]          # code, peer, channel, entry
+        self._host = torch.zeros(4, dtype=torch.int64).pin_memory()
+        self._event = torch.cuda.Event()
+        self._pending = False
+
+    def poll(self, raise_on_error: bool = True) -> Optional[dict]:
+        """Returns the decoded status when a requested copy has arrived (None otherwise)."""
+        if self._cpu:
+            return {"code": 0, "name": "ok"}
+        info = None
+        if self._pending and self._event.query():
+            self._pending = False
+            s = self._host.tolist()
+            info = {"code": int(s[0]), "peer": int(s[1]), "channel": int(s[2]), "entry": int(s[3]),
+                    "name": STATUS_NAMES.get(int(s[0]), str(s[0]))}
+            if raise_on_error and info["code"] != 0:
+                raise HelixTimeoutError(info["code"], info["peer"], info["channel"], info["entry"])
+        if not self._pending:
+            self._host.copy_(self._view, non_blocking=True)
+            self._event.record()
+            self._pending = True
+        return info
+
+
 def exchange_trace(workspace: torch.Tensor) -> torch.Tensor:
     """Device timeline of the LAST exchange launch on the workspace's device (needs ``HELIX_A2A_EXCHANGE_TRACE=1`` set
     before the first call): an ``[n, 8]`` int64 tensor of ``%globaltimer`` stamps, one row per CTA (= channel) in

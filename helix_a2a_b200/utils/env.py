@@ -79,9 +79,12 @@ def hook_timeout_ms() -> int:
         return 30000
 
 
-def hook_check() -> bool:
-    """``HELIX_A2A_HOOK_CHECK=0``: the import hook does not read the exchange's status after every engine step."""
-    return os.environ.get("HELIX_A2A_HOOK_CHECK", "1").strip() != "0"
+def hook_check_mode() -> str:
+    """``HELIX_A2A_HOOK_CHECK``: how the import hook watches the exchange's status after every engine step:
+    ``poll`` (default, any other value) = without waiting for the GPU, a failure is seen one or two steps late;
+    ``sync`` = read with a synchronisation every step; ``off`` (``0``) = not at all."""
+    v = os.environ.get("HELIX_A2A_HOOK_CHECK", "1").strip().lower()
+    return "off" if v in ("0", "off") else "sync" if v == "sync" else "poll"
 
 
 def handle_transport() -> str:

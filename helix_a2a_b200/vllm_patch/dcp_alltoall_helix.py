@@ -81,6 +81,24 @@ def dcp_a2a_check_status(raise_on_error: bool = True) -> dict:
     return _helix.check_status(_workspace, cp_rank, cp_size, raise_on_error=raise_on_error)
 
 
+_poller = None
+_poller_key = None
+
+
+def dcp_a2a_poll_status(raise_on_error: bool = True):
+    """Non-blocking form of :func:`dcp_a2a_check_status` for a call once per engine step: looks at the status copy
+    requested by the previous call (if it has arrived) and requests the next one; never waits for the GPU.  A
+    failure surfaces one or two steps late as ``HelixTimeoutError``."""
+    global _poller, _poller_key
+    if _workspace is None or _workspace_key is None:
+        return None
+    if _poller is None or _poller_key is not _workspace_key:
+        cp_size, cp_rank, _ = _workspace_key
+        _poller = _helix.StatusPoller(_workspace, cp_rank, cp_size)
+        _poller_key = _workspace_key
+    return _poller.poll(raise_on_error=raise_on_error)
+
+
 def _mnnvl_setting():
     v = _env.use_mnnvl()
     return False if v == "0" else True if v == "1" else "auto"

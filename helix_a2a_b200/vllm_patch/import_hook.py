@@ -78,13 +78,21 @@ def _ensure_before_capture() -> None:
 
 def _check_after_step() -> None:
     """A device-side wait of the native exchange that ran out must stop the engine, not go on serving the
-    NaN rows it left: read the status block once per step (64 bytes, after the step's own synchronisation)."""
+    NaN rows it left.  Once per step the status block is polled WITHOUT waiting for the GPU (a 32-byte copy to
+    pinned memory is requested and the previous one inspected), so a failure stops the engine one or two steps
+    late; ``HELIX_A2A_HOOK_CHECK=sync`` reads it with a synchronisation every step (costs ~0.25 ms per step of a
+    small model: the engine's asynchronous scheduling stalls), ``=0`` switches the check off."""
     if os.environ.get("HELIX_A2A_BACKEND", "nccl").lower() != "native":
         return
-    if os.environ.get("HELIX_A2A_HOOK_CHECK", "1").strip() == "0":
+    from helix_a2a_b200.utils import env as _env
+    mode = _env.hook_check_mode()
+    if mode == "off":
         return
     from helix_a2a_b200.vllm_patch import dcp_alltoall_helix as hx
-    hx.dcp_a2a_check_status(raise_on_error=True)
+    if mode == "sync":
+        hx.dcp_a2a_check_status(raise_on_error=True)
+    else:
+        hx.dcp_a2a_poll_status(raise_on_error=True)
 
 
 class _PatchingLoader(importlib.abc.Loader):

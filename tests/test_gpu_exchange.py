@@ -216,12 +216,23 @@ def test_timeout_in_combine_mode_leaves_nan_rows_and_hook_raises(helix):
         with pytest.raises(helix.HelixTimeoutError):
             hook.dcp_a2a_check_status()
         assert hook.dcp_a2a_check_status(raise_on_error=False)["code"] == 1
+        # the non-blocking poll the import hook runs once per engine step: the first call only requests a copy of
+        # the status block, a later one (the copy has arrived by then) raises
+        assert hook.dcp_a2a_poll_status() is None
+        torch.cuda.synchronize()
+        with pytest.raises(helix.HelixTimeoutError):
+            hook.dcp_a2a_poll_status()
     finally:
         hook._workspace, hook._workspace_key = old
+        hook._poller = None
     helix.init_workspace_all_rows(ws, cp)
     got, _ = _ops().alltoall_combine(outs, lses, ws, 0, cp, 0, False, False, 0, True, 0, 0)
     from helix_a2a_b200.ops import reference_math as rm
     assert (got.float() - rm.head_scatter_combine_reference(outs, lses)).abs().max() < 2e-2
+    poller = helix.StatusPoller(ws, 1, cp)            # a clean workspace polls clean
+    assert poller.poll() is None
+    torch.cuda.synchronize()
+    assert poller.poll()["code"] == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])

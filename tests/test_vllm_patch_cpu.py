@@ -106,7 +106,19 @@ def test_import_hook_checks_status_after_each_step(monkeypatch):
     mod = types.SimpleNamespace(Worker=Worker)
     import_hook._patch_worker_module(mod)
     monkeypatch.setenv("HELIX_A2A_BACKEND", "native")
-    monkeypatch.setattr(hook, "dcp_a2a_check_status", lambda raise_on_error=True: calls.append(raise_on_error))
-    assert Worker().execute_model(1) == 2 and calls == [True]
+    monkeypatch.delenv("HELIX_A2A_HOOK_CHECK", raising=False)
+    monkeypatch.setattr(hook, "dcp_a2a_check_status", lambda raise_on_error=True: calls.append(("sync", raise_on_error)))
+    monkeypatch.setattr(hook, "dcp_a2a_poll_status", lambda raise_on_error=True: calls.append(("poll", raise_on_error)))
+    # default: the status is polled without waiting for the GPU
+    assert Worker().execute_model(1) == 2 and calls == [("poll", True)]
+    monkeypatch.setenv("HELIX_A2A_HOOK_CHECK", "sync")
+    assert Worker().execute_model(1) == 2 and calls == [("poll", True), ("sync", True)]
     monkeypatch.setenv("HELIX_A2A_HOOK_CHECK", "0")
-    assert Worker().execute_model(1) == 2 and calls == [True]
+    assert Worker().execute_model(1) == 2 and len(calls) == 2
+
+
+def test_status_poller_on_cpu_workspace_is_a_no_op():
+    import helix_a2a_b200 as helix
+    ws = helix.allocate_workspace(1, 0, device="cpu")
+    poller = helix.StatusPoller(ws, 0, 1)
+    assert poller.poll()["code"] == 0
