@@ -155,6 +155,12 @@ __device__ __forceinline__ void oproj_cta(const OprojParams& p, uint8_t* smem_ra
       good = __shfl_sync(0xffffffffu, good, 0);
       ok = good != 0;
       if (!ok && lane == 0) fail(p, &s_abort);
+    } else {
+      // A CTA without any k-block has nothing that orders it behind the preceding kernel (no activation tile to wait
+      // for), but it writes a zero partial into scratch memory and counts itself in: under programmatic dependent
+      // launch that must not happen while the preceding launch (another o_proj on the same scratch, for instance)
+      // is still running.
+      asm volatile("griddepcontrol.wait;" ::: "memory");
     }
     tc_fence_after_sync();
     const int row = warp * 32 + lane;                 // TMEM lane == row of the W slab

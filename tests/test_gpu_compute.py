@@ -120,6 +120,25 @@ def test_oproj_matches_fp32_matmul(built, tokens, hidden, K, splits):
     assert err < 2e-2 * max(1.0, ref.abs().max().item()), err
 
 
+@pytest.mark.parametrize("hidden,K,splits,tokens", [(512, 256, 2, 300), (1024, 2048, 4, 300), (512, 256, 2, 17),
+                                                    (8192, 1024, 0, 8), (512, 256, -1, 300), (1024, 8192, 3, 300)])
+def test_oproj_back_to_back_under_programmatic_launch(built, monkeypatch, hidden, K, splits, tokens):
+    """Launches chained by programmatic dependent launch share the split-K scratch: a launch (a 256-token slice of a
+    larger call, or the next call) must not touch it before the previous one is done, not even from a CTA that has
+    no k-block of its own (512 x 256 in two splits with one 256-wide stage: the second split is empty)."""
+    from helix_a2a_b200.ops.oproj import oproj, check_compute_status
+    monkeypatch.setenv("HELIX_A2A_ENABLE_PDL", "1")
+    torch.manual_seed(tokens + K)
+    w = (torch.randn(hidden, K, device="cuda") * 0.02).bfloat16()
+    xs = [torch.randn(tokens, K, device="cuda").bfloat16() for _ in range(3)]
+    ys = [oproj(x, w, splits=splits) for x in xs]          # no synchronisation in between
+    torch.cuda.synchronize()
+    check_compute_status(xs[0])
+    for x, y in zip(xs, ys):
+        ref = x.float() @ w.float().t()
+        assert (y.float() - ref).abs().max() < 2e-2 * max(1.0, ref.abs().max().item())
+
+
 @pytest.mark.parametrize("tokens", [1, 8, 40, 200])
 @pytest.mark.parametrize("hidden,K,splits", [(8192, 1024, 0), (1024, 8192, 0), (512, 320, 1), (1152, 832, 2), (2048, 4096, 4)])
 def test_oproj_prepacked_weight_matches_fp32_matmul(built, tokens, hidden, K, splits):
