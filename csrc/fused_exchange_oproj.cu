@@ -7,13 +7,15 @@
 //   * Every other CTA is a GEMM CTA that owns one 128-row slab of W_o and one group of heads (a K-slice of
 //     at most 512: `heads_per_split` heads of D dims).  It first requests its whole W slice (<= 128 KB, one
 //     bulk copy per 64-wide atom when the weights are pre-packed): the weights do not depend on anything, so
-//     they stream while the other GPUs are still computing.  Then its four warps RECEIVE for themselves:
-//     for every (token, head of the group) they poll the lines of the N - 1 peers in the local rings
-//     (read-only: any number of CTAs may read the same lines), fold them with this rank's own row into the
-//     online LSE-weighted accumulator in registers and store the normalised bf16 row straight into shared
+//     they stream while the other GPUs are still computing.  Then its sixteen warps RECEIVE for themselves:
+//     for every (token, head of the group) a warp requests this rank's own row and the lines of the N - 1 peers
+//     in the local rings together (read-only: any number of CTAs may read the same lines; only sources whose
+//     flags are not all there yet are read again), folds them into the
+//     online LSE-weighted accumulator in registers and stores the normalised bf16 row straight into shared
 //     memory in the swizzled K-major layout the tensor core reads - the B operand of the UMMA.  One
 //     fence.proxy.async and a CTA barrier later a single thread issues the UMMAs (D[128, tokens] in TMEM);
-//     the epilogue and the split-K fold over the head groups are those of the stand-alone GEMM.
+//     four warps run the epilogue, and the split-K fold over the head groups is that of the stand-alone GEMM
+//     for up to 16 tokens (the slab's last CTA sums the partials).
 //   * The rings have many readers now, so nobody acknowledges lines while reading: every GEMM CTA counts
 //     itself out when it has read its last line, and the one that counts last publishes the consumed line
 //     counts of all rings of the call (locally, and by remote 8-byte stores to the senders).  A call uses a
