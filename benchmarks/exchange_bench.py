@@ -152,7 +152,10 @@ def make_paths(o, lse, ws, rank, world, hook, group, w_o=None):
         from helix_a2a_b200.ops.oproj import oproj
         import torch.nn.functional as F
         paths["oproj:helix_one_kernel"] = lambda: helix.alltoall_combine_oproj(o, lse, w_o, ws, rank, world)
-        paths["oproj:helix_two_kernels"] = lambda: oproj(helix.alltoall_combine(o, lse, ws, rank, world).reshape(B, -1), w_o)
+        paths["oproj:helix_two_kernels"] = lambda: oproj(helix.alltoall_combine(o, lse, ws, rank, world).reshape(B, -1), w_o,
+                                                         library=False)
+        # what a caller of alltoall_combine + ops.oproj gets by default: cuBLAS takes the product once it is compute-bound
+        paths["oproj:helix_exchange_auto_gemm"] = lambda: oproj(helix.alltoall_combine(o, lse, ws, rank, world).reshape(B, -1), w_o)
         paths["oproj:nccl_torch_linear"] = lambda: F.linear(nccl_torch().reshape(B, -1), w_o)
         if hook is not None:
             paths["oproj:reference_linear"] = lambda: F.linear(hook.dcp_a2a_lse_reduce(o, lse, cp).reshape(B, -1), w_o)

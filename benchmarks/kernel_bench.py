@@ -85,7 +85,7 @@ def main():
             if args.oproj_packed:
                 from helix_a2a_b200.ops.oproj import prepack_weight
                 wk = [prepack_weight(w) for w in ws]
-            fns = [(lambda l=l: oproj(x, wk[l], splits=args.oproj_splits)) for l in range(nl)]
+            fns = [(lambda l=l: oproj(x, wk[l], splits=args.oproj_splits, library=False)) for l in range(nl)]
             us = time_rotating(fns, args.iters)
             nbytes = hidden * K * 2 + tokens * K * 2 + tokens * hidden * 2
             rows.append({"kernel": "oproj", "tokens": tokens, "K": K, "us": us, "GBs": nbytes / us / 1e3,

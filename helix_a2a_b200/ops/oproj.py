@@ -5,14 +5,23 @@ matmul.  In the reference this is vLLM's cuBLAS linear layer.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 
-def oproj(x: torch.Tensor, w, *, splits: int = 0) -> torch.Tensor:
+def oproj(x: torch.Tensor, w, *, splits: int = 0, library: Optional[bool] = None) -> torch.Tensor:
     """``x [tokens, K]`` bf16, ``w [hidden, K]`` bf16 (``nn.Linear`` weight layout) -> bf16 ``[tokens, hidden]``.
 
     ``splits``: 0 lets the library pick (stream-K over all SMs when the plain grid would leave
     some idle), -1 forces the stream-K kernel, ``n >= 1`` forces the plain kernel with ``n`` K splits.
+
+    The hand-written kernel is built for decode: few tokens, bound by streaming W once (swap-AB, one 128-row slab
+    of W per CTA, every CTA reads all of x).  With many tokens the product is compute-bound and every slab's CTA
+    re-reads x, and cuBLAS is faster (measured on B200, hidden 8192: from 32 tokens at K >= 2048, 2x at 128
+    tokens; at K = 1024 from ~192 tokens).  So with ``splits=0`` and a plain weight matrix such calls go to
+    ``torch.nn.functional.linear``; ``library=False`` (or ``HELIX_A2A_OPROJ_LIBRARY=0``) keeps the hand-written
+    kernel for every size.  Packed weights always use the hand-written kernel (the plain matrix is not kept).
     """
     if isinstance(w, PackedOprojWeight):
         if not x.is_cuda:
@@ -21,8 +30,18 @@ def oproj(x: torch.Tensor, w, *, splits: int = 0) -> torch.Tensor:
         return ops().oproj_packed(x, w.packed, w.hidden, w.K, max(splits, 0))
     if not x.is_cuda:
         return (x.float() @ w.float().t()).to(x.dtype)
+    if splits == 0 and library is not False and library_gemm_pays(x.shape[0], w.shape[1]):
+        return torch.nn.functional.linear(x, w)
     from ._ext import ops
     return ops().oproj(x, w, splits)
+
+
+def library_gemm_pays(tokens: int, K: int) -> bool:
+    """The measured crossover between the decode kernel and cuBLAS (see :func:`oproj`)."""
+    from ..utils import env as _env
+    if not _env.oproj_library():
+        return False
+    return tokens >= (32 if K >= 2048 else 192)
 
 
 class PackedOprojWeight:

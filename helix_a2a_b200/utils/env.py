@@ -79,6 +79,12 @@ def hook_timeout_ms() -> int:
         return 30000
 
 
+def oproj_library() -> bool:
+    """``HELIX_A2A_OPROJ_LIBRARY=0``: ``ops.oproj`` never hands a large-token product to cuBLAS
+    (``torch.nn.functional.linear``); default: it does above the measured crossover."""
+    return os.environ.get("HELIX_A2A_OPROJ_LIBRARY", "1").strip() != "0"
+
+
 def hook_check_mode() -> str:
     """``HELIX_A2A_HOOK_CHECK``: how the import hook watches the exchange's status after every engine step:
     ``poll`` (default, any other value) = without waiting for the GPU, a failure is seen one or two steps late;

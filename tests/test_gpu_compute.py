@@ -107,8 +107,9 @@ def test_gqa_decode_small_group_base2_and_empty_sequence(built):
 @pytest.mark.parametrize("hidden,K,splits", [(8192, 1024, 0), (1024, 8192, 1), (512, 256, 2), (8192, 8192, 0),
                                              (8192, 8192, -1), (8192, 1024, -1), (512, 256, -1), (1152, 832, -1),
                                              (1024, 8192, 3), (512, 4096, 8), (1024, 2048, 4)])
-def test_oproj_matches_fp32_matmul(built, tokens, hidden, K, splits):
+def test_oproj_matches_fp32_matmul(built, monkeypatch, tokens, hidden, K, splits):
     from helix_a2a_b200.ops.oproj import oproj, check_compute_status
+    monkeypatch.setenv("HELIX_A2A_OPROJ_LIBRARY", "0")     # the hand-written kernel at every size
     torch.manual_seed(tokens + hidden)
     x = torch.randn(tokens, K, device="cuda").bfloat16()
     w = (torch.randn(hidden, K, device="cuda") * 0.02).bfloat16()
@@ -128,6 +129,7 @@ def test_oproj_back_to_back_under_programmatic_launch(built, monkeypatch, hidden
     no k-block of its own (512 x 256 in two splits with one 256-wide stage: the second split is empty)."""
     from helix_a2a_b200.ops.oproj import oproj, check_compute_status
     monkeypatch.setenv("HELIX_A2A_ENABLE_PDL", "1")
+    monkeypatch.setenv("HELIX_A2A_OPROJ_LIBRARY", "0")
     torch.manual_seed(tokens + K)
     w = (torch.randn(hidden, K, device="cuda") * 0.02).bfloat16()
     xs = [torch.randn(tokens, K, device="cuda").bfloat16() for _ in range(3)]
@@ -137,6 +139,23 @@ def test_oproj_back_to_back_under_programmatic_launch(built, monkeypatch, hidden
     for x, y in zip(xs, ys):
         ref = x.float() @ w.float().t()
         assert (y.float() - ref).abs().max() < 2e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_oproj_hands_compute_bound_sizes_to_the_library(built, monkeypatch):
+    """splits=0 with a plain weight: above the measured crossover the product goes to cuBLAS (same result within
+    bf16 rounding); below it, with packed weights, or with HELIX_A2A_OPROJ_LIBRARY=0 the hand-written kernel runs."""
+    from helix_a2a_b200.ops import oproj as om
+    monkeypatch.delenv("HELIX_A2A_OPROJ_LIBRARY", raising=False)
+    assert not om.library_gemm_pays(8, 8192) and om.library_gemm_pays(32, 2048) and not om.library_gemm_pays(64, 1024)
+    assert om.library_gemm_pays(256, 1024)
+    x = torch.randn(96, 2048, device="cuda").bfloat16()
+    w = (torch.randn(1024, 2048, device="cuda") * 0.02).bfloat16()
+    y_lib = om.oproj(x, w)
+    monkeypatch.setenv("HELIX_A2A_OPROJ_LIBRARY", "0")
+    assert not om.library_gemm_pays(96, 2048)
+    y_own = om.oproj(x, w)
+    ref = x.float() @ w.float().t()
+    assert (y_lib.float() - ref).abs().max() < 2e-2 and (y_own.float() - ref).abs().max() < 2e-2
 
 
 @pytest.mark.parametrize("tokens", [1, 8, 40, 200])
