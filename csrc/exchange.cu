@@ -161,6 +161,9 @@ cudaError_t initialize_workspace_row(uint64_t* local_row, int cp_size, int sm_co
 // (csrc/helix_alltoall.cu:524-530); for decode the right count depends on how many entries
 // a call carries: few entries -> one entry per channel and several warps per entry (latency),
 // many entries -> one channel per SM and one warp per entry (bandwidth).
+// lines one channel moves per call from which the warps of a CTA are re-balanced towards receiving
+constexpr int kBulkLinesPerChannel = 192;
+
 LaunchInfo plan_launch(const ExchangeParams& p, int channel_override) {
   LaunchInfo li{};
   const int N = p.cp_size;
@@ -182,7 +185,15 @@ LaunchInfo plan_launch(const ExchangeParams& p, int channel_override) {
   if (p.mode == kModeCombine) {
     // few entries per channel: let up to 4 warps share an entry, each polling a subset of peers
     if (per_channel <= 2 && N > 2 && li.iters <= 3) group = std::min(4, N - 1);
-    int groups = std::max(1, std::min(per_channel, kMaxRecvWarps / group));
+    int max_recv = kMaxRecvWarps;
+    if (N > 1 && (int64_t)per_channel * L >= kBulkLinesPerChannel) {
+      // Many lines per channel: the call is bound by throughput, and the receive side (own row, poll, combine,
+      // store: one message per warp at a time) is the slower one; the senders keep up with fewer warps.  Of the 16
+      // warps of a CTA about 6 send and the rest receive.
+      li.send_warps = (N - 1) * std::max(1, 6 / (N - 1));
+      max_recv = 16 - li.send_warps;
+    }
+    int groups = std::max(1, std::min(per_channel, max_recv / group));
     if (group > 1) groups = std::min(groups, 2);
     recv = groups * group;
   } else {
