@@ -102,6 +102,28 @@ def test_fused_combine_native_layout(helix, cp, B, H, D, base2):
     assert (glse - wlse).abs().max() < 1e-4
 
 
+@pytest.mark.parametrize("cp", [2, 4, 8])
+def test_fused_combine_bulk_call(helix, cp):
+    """Hundreds of lines per channel: the auto-tuner gives 10 (cp = 8: 9) of a CTA's 16 warps to receiving."""
+    from helix_a2a_b200.ops import reference_math as rm
+    from helix_a2a_b200.ops._ext import ext
+    B, H, D = 32 * cp, 128, 512          # >= 22 entries per channel of 9 lines each, whatever the rank count
+    torch.manual_seed(cp)
+    ws = _ws(helix, cp)
+    outs = torch.randn(cp, B, H, D, device="cuda").bfloat16()
+    lses = torch.randn(cp, B, H, device="cuda") * 3
+    for _ in range(2):
+        got, glse = _ops().alltoall_combine(outs, lses, ws, 0, cp, 0, True, False, 0, True, 0, 0)
+    torch.cuda.synchronize()
+    info = ext().last_launch_info()
+    assert info["recv_warps"] > 8 and info["send_warps"] + info["recv_warps"] == 16
+    want, wlse = rm.head_scatter_combine_reference(outs, lses, return_lse=True)
+    assert (got.float() - want).abs().max() < 2e-2
+    assert (glse - wlse).abs().max() < 1e-4
+    for r in range(cp):
+        assert helix.check_status(ws, r, cp)["code"] == 0
+
+
 @pytest.mark.parametrize("stats_mode", ["lse", "max_sumexp"])
 def test_fused_combine_entries_layout_and_stats_modes(helix, stats_mode):
     from helix_a2a_b200.ops import reference_math as rm
