@@ -29,21 +29,43 @@ def measured_peaks():
         return 6650.0, 1590.0, "fallback"
 
 
-def time_rotating(fns, iters, warmup=3):
+def time_rotating(fns, iters, warmup=3, graph=True):
+    """Device time per call in us: the calls (one per rotating buffer, so that nothing is found in L2) are captured
+    into ONE CUDA graph that is replayed ``iters`` times between two events, so the host's launch cost (10-25 us per
+    op call from Python, more than a small kernel runs) is not in the number.  ``graph=False`` times eager calls."""
     for _ in range(warmup):
         for f in fns:
             f()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    n = 0
-    for _ in range(iters):
+    if not graph:
+        e0.record()
+        for _ in range(iters):
+            for f in fns:
+                f()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (iters * len(fns)) * 1e3
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
         for f in fns:
             f()
-            n += 1
+        side.synchronize()
+        with torch.cuda.graph(g, stream=side):
+            for f in fns:
+                f()
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(warmup):
+        g.replay()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        g.replay()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / n * 1e3   # us
+    return e0.elapsed_time(e1) / (iters * len(fns)) * 1e3   # us
 
 
 def main():

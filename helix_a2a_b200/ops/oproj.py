@@ -18,8 +18,8 @@ def oproj(x: torch.Tensor, w, *, splits: int = 0, library: Optional[bool] = None
 
     The hand-written kernel is built for decode: few tokens, bound by streaming W once (swap-AB, one 128-row slab
     of W per CTA, every CTA reads all of x).  With many tokens the product is compute-bound and every slab's CTA
-    re-reads x, and cuBLAS is faster (measured on B200, hidden 8192: from 32 tokens at K >= 2048, 2x at 128
-    tokens; at K = 1024 from ~192 tokens).  So with ``splits=0`` and a plain weight matrix such calls go to
+    re-reads x, and cuBLAS is faster (measured on B200 inside CUDA graphs, hidden 8192: level up to 8 tokens, 10-40 %
+    ahead at 32-64 tokens, 2x at 128).  So with ``splits=0`` and a plain weight matrix calls of 32 tokens or more go to
     ``torch.nn.functional.linear``; ``library=False`` (or ``HELIX_A2A_OPROJ_LIBRARY=0``) keeps the hand-written
     kernel for every size.  Packed weights always use the hand-written kernel (the plain matrix is not kept).
     """
@@ -41,7 +41,8 @@ def library_gemm_pays(tokens: int, K: int) -> bool:
     from ..utils import env as _env
     if not _env.oproj_library():
         return False
-    return tokens >= (32 if K >= 2048 else 192)
+    del K          # the crossover does not depend on it: 32 tokens at K = 1024 ... 8192
+    return tokens >= 32
 
 
 class PackedOprojWeight:

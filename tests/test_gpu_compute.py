@@ -146,8 +146,8 @@ def test_oproj_hands_compute_bound_sizes_to_the_library(built, monkeypatch):
     bf16 rounding); below it, with packed weights, or with HELIX_A2A_OPROJ_LIBRARY=0 the hand-written kernel runs."""
     from helix_a2a_b200.ops import oproj as om
     monkeypatch.delenv("HELIX_A2A_OPROJ_LIBRARY", raising=False)
-    assert not om.library_gemm_pays(8, 8192) and om.library_gemm_pays(32, 2048) and not om.library_gemm_pays(64, 1024)
-    assert om.library_gemm_pays(256, 1024)
+    assert not om.library_gemm_pays(8, 8192) and not om.library_gemm_pays(31, 1024)
+    assert om.library_gemm_pays(32, 2048) and om.library_gemm_pays(256, 1024)
     x = torch.randn(96, 2048, device="cuda").bfloat16()
     w = (torch.randn(1024, 2048, device="cuda") * 0.02).bfloat16()
     y_lib = om.oproj(x, w)
