@@ -330,7 +330,8 @@ def test_public_api_cp1(helix):
                                               (4, 64, 16, 128, 512), (8, 8, 64, 128, 1024), (8, 33, 64, 128, 256),
                                               (2, 5, 8, 64, 384), (3, 2, 12, 192, 128),
                                               # many rows: the slabs of a head group share them, token-sliced fold
-                                              (2, 64, 16, 128, 1024), (4, 40, 32, 128, 1024), (2, 17, 32, 128, 512)])
+                                              (2, 64, 16, 128, 1024), (4, 40, 32, 128, 1024), (2, 17, 32, 128, 512),
+                                              (2, 20, 12, 128, 256)])      # three heads per group
 def test_fused_exchange_combine_oproj(helix, cp, B, H, D, hidden):
     """One launch: exchange + combine + tcgen05 o_proj, all ranks played on one GPU."""
     from helix_a2a_b200.ops import reference_math as rm
