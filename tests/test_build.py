@@ -50,3 +50,21 @@ def test_one_kernel_path_shape_rules(native_built):
     assert not fits(8, 16, 512, 7168, 8)     # MLA rows (512 dims) are 9 lines, more than one warp-wide load
     assert not fits(8, 8, 128, 8192, 16)     # at most 8 ranks
     assert not fits(8, 64, 128, 8192, 1)     # a single rank has nothing to exchange
+
+
+def test_bench_defaults_and_config_keys(monkeypatch):
+    """bench.py without flags: one GPU, at least three warm-up steps, the two-kernel chain; both arms print the same
+    ``config`` keys (they share the function that builds it); --fuse-oproj alone means "on"."""
+    import sys
+    import bench
+    monkeypatch.setattr(sys, "argv", ["bench.py"])
+    a = bench.parse()
+    assert a.gpus == 1 and a.warmup >= 3 and a.steps >= 1 and a.impl == "helix" and a.fuse_oproj == "off"
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--fuse-oproj", "--impl", "reference"])
+    a = bench.parse()
+    assert a.fuse_oproj == "on" and a.impl == "reference"
+    cfg = bench.bench_config(80, 8, 131072, 8, 16, 16384, 42_900_000_000, True)
+    assert {"model", "global_batch", "seq_len", "parallelism"} <= set(cfg) and cfg["parallelism"] == "cp8"
+    import inspect
+    from benchmarks import reference_arm
+    assert "bench_config(" in inspect.getsource(reference_arm)
