@@ -1,5 +1,6 @@
 #!/usr/bin/env python
-"""Per-CTA device timeline of the GQA decode attention kernel (1 GPU).
+"""Per-CTA device timeline of the GQA decode attention kernel (1 GPU).  The reference has no attention kernel of its
+own: vLLM supplies it, and the reference's hook starts from the attention output (patches/dcp_alltoall_helix.py:511-600).
 
     HELIX_A2A_ATTN_TRACE=1 python benchmarks/attn_timeline.py [--shapes 1x131072,8x16384] [--per-sm]
 

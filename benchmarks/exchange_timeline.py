@@ -1,6 +1,10 @@
 #!/usr/bin/env python
 """Device timeline of the fused exchange + combine kernel on real GPUs (one rank per GPU, torchrun).
 
+The reference looks inside a call with nsys around its benchmark (benchmark/scripts/benchmark_helix_pipeline.py:30-31,
+benchmark/sbatch/pipeline_bench.sbatch:167-170); nsys is not available where this library is developed, so the
+kernel stamps %globaltimer itself.
+
     HELIX_A2A_EXCHANGE_TRACE=1 torchrun --nproc-per-node N benchmarks/exchange_timeline.py [--shape gqa|mla] [--tokens 8,256]
 
 Every CTA (= channel) of the kernel records %globaltimer stamps (kernel entry, first / last line posted, first /

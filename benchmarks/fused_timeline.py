@@ -1,5 +1,6 @@
 #!/usr/bin/env python
-"""Device timeline of the one-kernel exchange + combine + o_proj.
+"""Device timeline of the one-kernel exchange + combine + o_proj (the counterpart of an nsys timeline of the
+reference's pipeline, benchmark/sbatch/pipeline_bench.sbatch:167-170; the kernel stamps %globaltimer itself).
 
 Real ranks (one per GPU):
     HELIX_A2A_EXCHANGE_TRACE=1 torchrun --nproc-per-node N benchmarks/fused_timeline.py [--tokens 1,8,32,64] [--hidden 2048]

@@ -1,4 +1,7 @@
 // Debug bounds checks of the exchange's addressing of USER tensors (ring offsets are modulo by construction).
+// The reference validates shapes, dtypes and contiguity on the host only (csrc/torch_binding.cpp:75-113) and its
+// kernel takes dense [entries, cp, D] buffers (csrc/helix_alltoall.cu:292-309), so it has no counterpart of these
+// checks; here the kernel addresses strided views of the caller's tensors, which is what they cover.
 //
 // The kernel reads its inputs in their native strided layout and writes its outputs through strides that the
 // binding computes; a wrong stride would read or write outside the caller's tensors.  With

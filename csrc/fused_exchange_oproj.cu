@@ -1,4 +1,7 @@
 // Helix exchange + LSE combine + o_proj in ONE kernel (sm_100a).
+// In the reference these are three steps on three code paths: its all-to-all kernel (csrc/helix_alltoall.cu:194-474),
+// its Triton combine (patches/dcp_alltoall_helix.py:210-384) behind the hook's layout copies (:511-600), and vLLM's
+// cuBLAS o_proj.
 //
 // With a few rows per call the combined activation never exists in global memory and no CTA waits for another
 // CTA of its own GPU; with many rows the slabs of a head group share the receive work (last paragraph):
