@@ -507,5 +507,21 @@ PYBIND11_MODULE(_C, m) {
     return d;
   });
   m.def("wire_bytes", [](int payload_bytes) { return helix::ll128::wire_bytes_for_words((payload_bytes + 7) / 8); });
+  // what the auto-tuner would choose for a call (no launch, no GPU): entries = outer * inner rows of o_bytes + stats
+  m.def("plan_info", [](int cp, int sm_count, int outer, int inner, int o_bytes, int st_words, bool combine) {
+    helix::ExchangeParams p{};
+    p.cp_size = cp; p.sm_count = sm_count; p.outer = outer; p.inner = inner; p.o_bytes = o_bytes; p.st_words = st_words;
+    p.mode = combine ? helix::kModeCombine : helix::kModeExchange;
+    p.ranks_in_launch = 1;
+    helix::LaunchInfo li = helix::plan_launch(p, 0);
+    py::dict d;
+    d["channels"] = li.channels;
+    d["send_warps"] = li.send_warps;
+    d["recv_warps"] = li.recv_warps;
+    d["group_warps"] = li.group_warps;
+    d["lines_per_message"] = li.lines_per_message;
+    d["iters"] = li.iters;
+    return d;
+  });
   bind_compute(m);
 }

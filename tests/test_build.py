@@ -68,3 +68,22 @@ def test_bench_defaults_and_config_keys(monkeypatch):
     import inspect
     from benchmarks import reference_arm
     assert "bench_config(" in inspect.getsource(reference_arm)
+
+
+def test_exchange_auto_tuner_plans(native_built):
+    """The launch shapes the auto-tuner picks (csrc/exchange.cu::plan_launch), without a GPU.  The reference derives
+    its channel count from the SM count alone (csrc/helix_alltoall.cu:524-530); here it follows the entry count."""
+    from helix_a2a_b200.ops._ext import ext
+    plan = ext().plan_info                     # (cp, SMs, outer, heads per rank, row bytes, stats words, combine)
+    # one decode token at cp = 2: one entry per channel, every sender warp on the single peer, one receiver warp
+    p = plan(2, 148, 1, 32, 256, 1, True)
+    assert (p["channels"], p["send_warps"], p["recv_warps"], p["lines_per_message"]) == (32, 8, 1, 3)
+    # cp = 8, one entry per channel: four receiver warps share the entry's seven peers
+    p = plan(8, 148, 8, 8, 256, 1, True)
+    assert (p["channels"], p["send_warps"], p["group_warps"], p["recv_warps"]) == (64, 7, 4, 4)
+    # hundreds of lines per channel: 6 of the CTA's 16 warps send, 10 receive (cp = 8: one per peer, 7 + 9)
+    for cp, want in ((2, (6, 10)), (4, (6, 10)), (8, (7, 9))):
+        p = plan(cp, 148, 256, 128 // cp, 1024, 1, True)
+        assert p["channels"] == 148 and (p["send_warps"], p["recv_warps"]) == want and p["lines_per_message"] == 9
+    # exchange-only mode keeps eight receiver warps
+    assert plan(4, 148, 64, 32, 1024, 4, False)["recv_warps"] == 8
