@@ -28,6 +28,7 @@ EXTENSION_KNOBS = {
     "HELIX_A2A_ATTN_TRACE": ("0", "1: the GQA decode kernel records per-CTA %globaltimer stamps, SM id and chunk counts"),
     "HELIX_A2A_ATTN_DYN_PCT": ("unset", "percent of every long (sequence, kv head) pair handed out dynamically; 0: fixed shares"),
     "HELIX_A2A_ATTN_DYN_CHUNK": ("unset", "blocks of 16 tokens per dynamically drawn chunk"),
+    "HELIX_A2A_ATTN_DYN_MIN_BLOCKS": ("unset", "only (sequence, kv head) pairs with at least this many 16-token blocks get a pool (default 64)"),
     "HELIX_A2A_MLA_VARIANT": ("ws", "ws: producer + math warps; lockstep: all warps walk a tile's phases together"),
     "HELIX_A2A_MLA_PROF": ("0", "1: the lockstep MLA kernel sums clock64 per phase of its tile loop"),
 }
