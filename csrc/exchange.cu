@@ -13,6 +13,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -161,8 +162,13 @@ cudaError_t initialize_workspace_row(uint64_t* local_row, int cp_size, int sm_co
 // (csrc/helix_alltoall.cu:524-530); for decode the right count depends on how many entries
 // a call carries: few entries -> one entry per channel and several warps per entry (latency),
 // many entries -> one channel per SM and one warp per entry (bandwidth).
-// lines one channel moves per call from which the warps of a CTA are re-balanced towards receiving
-constexpr int kBulkLinesPerChannel = 192;
+// lines one channel moves per call from which the warps of a CTA are re-balanced towards receiving (measured at
+// two ranks: 192, 96 and 48 lines are each better than the next larger value for the calls they add)
+constexpr int kBulkLinesPerChannelDefault = 48;
+static int bulk_lines_per_channel() {
+  if (const char* v = std::getenv("HELIX_A2A_BULK_LINES")) return std::max(1, std::atoi(v));
+  return kBulkLinesPerChannelDefault;
+}
 
 LaunchInfo plan_launch(const ExchangeParams& p, int channel_override) {
   LaunchInfo li{};
@@ -186,11 +192,15 @@ LaunchInfo plan_launch(const ExchangeParams& p, int channel_override) {
     // few entries per channel: let up to 4 warps share an entry, each polling a subset of peers
     if (per_channel <= 2 && N > 2 && li.iters <= 3) group = std::min(4, N - 1);
     int max_recv = kMaxRecvWarps;
-    if (N > 1 && (int64_t)per_channel * L >= kBulkLinesPerChannel) {
+    if (N > 1 && (int64_t)per_channel * L >= bulk_lines_per_channel()) {
       // Many lines per channel: the call is bound by throughput, and the receive side (own row, poll, combine,
       // store: one message per warp at a time) is the slower one; the senders keep up with fewer warps.  Of the 16
-      // warps of a CTA about 6 send and the rest receive.
-      li.send_warps = (N - 1) * std::max(1, 6 / (N - 1));
+      // warps of a CTA 4 (two ranks; measured best of 1..7 there: MLA rows, 256 tokens, 35 us against 45 with 6 and
+      // 55 with 2) or about 6 (more ranks: at least one per peer) send and the rest receive.
+      // HELIX_A2A_BULK_SEND_WARPS / HELIX_A2A_BULK_LINES override the two numbers for experiments.
+      int bulk_send = N == 2 ? 4 : 6;
+      if (const char* v = std::getenv("HELIX_A2A_BULK_SEND_WARPS")) bulk_send = std::max(1, std::min(12, std::atoi(v)));
+      li.send_warps = (N - 1) * std::max(1, bulk_send / (N - 1));
       max_recv = 16 - li.send_warps;
     }
     int groups = std::max(1, std::min(per_channel, max_recv / group));

@@ -81,8 +81,8 @@ def test_exchange_auto_tuner_plans(native_built):
     # cp = 8, one entry per channel: four receiver warps share the entry's seven peers
     p = plan(8, 148, 8, 8, 256, 1, True)
     assert (p["channels"], p["send_warps"], p["group_warps"], p["recv_warps"]) == (64, 7, 4, 4)
-    # hundreds of lines per channel: 6 of the CTA's 16 warps send, 10 receive (cp = 8: one per peer, 7 + 9)
-    for cp, want in ((2, (6, 10)), (4, (6, 10)), (8, (7, 9))):
+    # many lines per channel: 4 (two ranks) or 6 of the CTA's 16 warps send, the rest receive (cp = 8: one per peer, 7 + 9)
+    for cp, want in ((2, (4, 12)), (4, (6, 10)), (8, (7, 9))):
         p = plan(cp, 148, 256, 128 // cp, 1024, 1, True)
         assert p["channels"] == 148 and (p["send_warps"], p["recv_warps"]) == want and p["lines_per_message"] == 9
     # exchange-only mode keeps eight receiver warps
