@@ -163,8 +163,8 @@ cudaError_t initialize_workspace_row(uint64_t* local_row, int cp_size, int sm_co
 // a call carries: few entries -> one entry per channel and several warps per entry (latency),
 // many entries -> one channel per SM and one warp per entry (bandwidth).
 // lines one channel moves per call from which the warps of a CTA are re-balanced towards receiving (measured at
-// two ranks: 192, 96 and 48 lines are each better than the next larger value for the calls they add)
-constexpr int kBulkLinesPerChannelDefault = 48;
+// two ranks: 192, 96, 48 and 24 lines are each at least as good as the next larger value for the calls they add)
+constexpr int kBulkLinesPerChannelDefault = 24;
 static int bulk_lines_per_channel() {
   if (const char* v = std::getenv("HELIX_A2A_BULK_LINES")) return std::max(1, std::atoi(v));
   return kBulkLinesPerChannelDefault;

@@ -22,7 +22,7 @@ EXTENSION_KNOBS = {
     "HELIX_A2A_CHANNEL_COUNT": ("0", "0 / unset: the auto-tuner picks the exchange's channel count; n: exactly n"),
     "HELIX_A2A_TIMEOUT_MS": ("2000", "time limit of every device-side wait of a call that does not pass its own"),
     "HELIX_A2A_DEBUG": ("0", "1: exchange outputs are pre-filled with NaN so that an unwritten row shows"),
-    "HELIX_A2A_BULK_LINES": ("48", "lines per channel and call from which the exchange gives more of a CTA's warps to receiving"),
+    "HELIX_A2A_BULK_LINES": ("24", "lines per channel and call from which the exchange gives more of a CTA's warps to receiving"),
     "HELIX_A2A_BULK_SEND_WARPS": ("4 / 6", "sender warps per CTA for such calls (two ranks / more ranks)"),
     "HELIX_A2A_OPROJ_STREAMK": ("unset", "1 / 0: force / forbid the stream-K o_proj kernel where the library would choose"),
     "HELIX_A2A_OPROJ_TRACE": ("0", "1: the stream-K o_proj kernel records %globaltimer stamps per CTA"),
